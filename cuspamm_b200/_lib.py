@@ -1,0 +1,110 @@
+"""ctypes binding of libspamm.so (the C ABI declared in include/spamm.h).
+
+There is no CPU fallback: if the library is missing it is built with nvcc, and if that fails the import of
+this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from . import build as _build
+
+_PKG = Path(__file__).resolve().parent
+
+
+class SpammStats(C.Structure):
+    """Mirror of `spamm_stats` in include/spamm.h."""
+
+    _fields_ = [
+        ("ms_h2d", C.c_float),
+        ("ms_norm", C.c_float),
+        ("ms_lists", C.c_float),
+        ("ms_pack", C.c_float),
+        ("ms_multiply", C.c_float),
+        ("ms_d2h", C.c_float),
+        ("ms_device_total", C.c_float),
+        ("survivors", C.c_int64),
+        ("tile_products", C.c_int64),
+        ("steps", C.c_int64),
+        ("packed_tiles_a", C.c_int64),
+        ("packed_tiles_b", C.c_int64),
+        ("executed_flops", C.c_double),
+    ]
+
+    def as_dict(self) -> dict:
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+_vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+_pp = C.POINTER(C.c_void_p)
+
+# name -> (restype, argtypes); every symbol include/spamm.h declares
+SIGNATURES = {
+    "spamm_plan_create": (_i, [_pp, _i, _i, _i, _i, _i, _i]),
+    "spamm_plan_destroy": (_i, [_vp]),
+    "spamm_upload": (_i, [_vp, _vp, _vp]),
+    "spamm_norms": (_i, [_vp]),
+    "spamm_norms_share": (_i, [_vp, _i, _i]),
+    "spamm_build_lists": (_i, [_vp, _f]),
+    "spamm_pack": (_i, [_vp]),
+    "spamm_gated_multiply": (_i, [_vp]),
+    "spamm_run": (_i, [_vp, _f]),
+    "spamm_sync": (_i, [_vp]),
+    "spamm_download_c": (_i, [_vp, _vp]),
+    "spamm_multiply": (_i, [_vp, _vp, _vp, _vp, _f, C.POINTER(SpammStats)]),
+    "spamm_run_timed": (_i, [_vp, _f, C.POINTER(SpammStats)]),
+    "spamm_get_norm_a": (_i, [_vp, _vp]),
+    "spamm_get_norm_b": (_i, [_vp, _vp]),
+    "spamm_get_counts": (_i, [_vp, _vp, C.POINTER(_i64)]),
+    "spamm_get_lists": (_i, [_vp, _vp, _vp]),
+    "spamm_device_buffer": (_i, [_vp, _i, _pp, C.POINTER(_sz)]),
+    "spamm_stream": (_i, [_vp, _pp]),
+    "spamm_plan_dims": (_i, [_vp] + [C.POINTER(_i)] * 5),
+    "spamm_norm_map_dev": (_i, [_vp, _i, _i, _i64, _vp, _vp]),
+    "spamm_build_lists_dev": (_i, [_vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "spamm_pack_half_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "spamm_gated_multiply_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i64, _vp, _vp]),
+    "spamm_gen_decay_exp": (_i, [_vp, _f, _f, _i64, _i64, _i64]),
+    "spamm_gen_decay_alg": (_i, [_vp, _f, _f, _i64, _i64, _i64]),
+    "spamm_gen_signed_exp": (_i, [_vp, C.c_double, C.c_uint64, _i64, _i64, _i64]),
+    "spamm_gen_uniform_alg": (_i, [_vp, C.c_uint64, _i64, _i64, _i64]),
+    "spamm_gen_uniform": (_i, [_vp, C.c_uint64, _i64, _i64, _i64]),
+    "spamm_gen_lattice": (_i, [_vp, _i, C.c_uint64, _i64, _i64]),
+    "spamm_status_string": (C.c_char_p, [_i]),
+    "spamm_last_cuda_error": (C.c_char_p, []),
+    "spamm_kernel_launches": (_i64, [_vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads (building first if needed) libspamm.so and sets the argument types of every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not path.exists():
+        path = _build.build_library()
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class SpammError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        lib = load()
+        msg = lib.spamm_status_string(status).decode()
+        detail = lib.spamm_last_cuda_error().decode()
+        super().__init__(f"{where}: {msg} (status {status})" + (f": {detail}" if detail and status in (2, 3) else ""))
+        self.status = status
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise SpammError(status, where)

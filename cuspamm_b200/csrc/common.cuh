@@ -1,0 +1,37 @@
+// Shared constants and small helpers of the SpAMM kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/spamm.h"
+
+namespace spamm {
+
+constexpr int TILE = SPAMM_TILE;                 // 32, LoNum of the reference (main.h:32)
+constexpr int MT_R = SPAMM_MT_ROWS;              // C tiles per macro tile, vertically
+constexpr int MT_C = SPAMM_MT_COLS;              // C tiles per macro tile, horizontally
+constexpr int TILE_BYTES = TILE * TILE * 2;      // one packed half tile
+constexpr int A_SLAB_BYTES = MT_R * TILE_BYTES;  // 8 KiB: 128 rows x 32 k
+constexpr int B_SLAB_BYTES = MT_C * TILE_BYTES;  // 16 KiB: 256 columns x 32 k
+constexpr int STEP_CAP_PER_K = 8;                // a k yields at most 8 steps (one per tile column)
+
+// step word: bits 0-15 k, 16-19 row mask, 20-27 column mask
+__host__ __device__ inline uint32_t step_pack(uint32_t k, uint32_t rows, uint32_t cols) {
+    return (k & 0xffffu) | ((rows & 0xfu) << 16) | ((cols & 0xffu) << 20);
+}
+__host__ __device__ inline uint32_t step_k(uint32_t s) { return s & 0xffffu; }
+__host__ __device__ inline uint32_t step_rows(uint32_t s) { return (s >> 16) & 0xfu; }
+__host__ __device__ inline uint32_t step_cols(uint32_t s) { return (s >> 20) & 0xffu; }
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Records a CUDA error for spamm_last_cuda_error and maps it to a status.
+int record_cuda_error(cudaError_t e, const char *what);
+
+#define SPAMM_CUDA_TRY(call)                                                    \
+    do {                                                                        \
+        cudaError_t e__ = (call);                                               \
+        if (e__ != cudaSuccess) return ::spamm::record_cuda_error(e__, #call);  \
+    } while (0)
+
+}  // namespace spamm

@@ -1,0 +1,431 @@
+// Gated block multiply on the 5th-generation tensor cores (tcgen05 + tensor memory), sm_100a only.
+//
+// Stands in for get_C_FP16_B32 (reference cuSpAMM.cu:336-391): for every C tile, the sum over the surviving k of
+// half(A(i,k)) * half(B(k,j)) with float accumulation; tiles with an empty list are written as zeros
+// (cuSpAMM.cu:300,391).  The reference runs one 128-thread block per 32x32 C tile with 16x16x16 WMMA fragments.
+// Here a persistent block per SM walks macro tiles of 128 x 256 C elements (4 x 8 tiles):
+//
+//   warp 0      producer: reads the macro tile's step list and issues bulk copies (cp.async.bulk, completion on
+//               an mbarrier) of the packed half tiles a step names into a ring of shared-memory stages;
+//   warp 1      one elected thread issues tcgen05.mma (M=128, N=32*run, K=16) per run of adjacent tile columns
+//               of a step; the step's row set becomes the instruction's disable-output-lane mask, so tile rows
+//               that did not survive are not touched -- no product outside the lists is ever added;
+//   warps 2-5   epilogue: read the 128x256 float accumulator from tensor memory (tcgen05.ld), store it to C,
+//               clear it for the next macro tile; macro tiles without any step are written as zeros directly.
+//
+// Two accumulators (2 x 256 of the 512 tensor-memory columns) let the epilogue of one macro tile overlap the
+// multiplies of the next.  Every wait on an mbarrier is bounded in time; when one runs out the block sets the
+// error word, drains its copies and multiplies, frees its tensor memory and returns.
+#include "common.cuh"
+
+namespace spamm {
+
+constexpr int STAGES = 6;
+constexpr int STAGE_BYTES = A_SLAB_BYTES + B_SLAB_BYTES;   // 24 KiB
+constexpr int GM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t ACC_COLS = MT_C * TILE;                  // 256
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
+constexpr int SMEM_CTRL_BYTES = 256;
+constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 128;
+
+struct Ctrl {
+    unsigned long long full[STAGES];
+    unsigned long long empty[STAGES];
+    unsigned long long tmem_full[2];
+    unsigned long long tmem_empty[2];
+    unsigned long long drain;
+    uint32_t step_word[STAGES];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase of `bar` with the given parity to complete, at most WAIT_LIMIT_NS.
+__device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int32_t *err,
+                                       int code)
+{
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            atomicCAS(err, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                             int32_t *err, int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    return wait_slow(bar, parity, abort_flag, err, code);
+}
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// K-major, no swizzle: 8-row groups 512 B apart (SBO), the two 8-element k chunks of a K=16 step 128 B apart (LBO).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
+{
+    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | ((128u >> 4) << 16);
+    const uint32_t hi = (512u >> 4) | (1u << 14);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%4, %5, %6, %7}, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32_zero(uint32_t taddr)
+{
+    const uint32_t z = 0;
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+        "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
+        "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_TMEM_EMPTY = 3, ERR_WAIT_TMEM_FULL = 4, ERR_WAIT_DRAIN = 5 };
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restrict__ half_b,
+                      const uint32_t *__restrict__ steps, const int32_t *__restrict__ step_counts,
+                      const int32_t *__restrict__ order, int row_tiles, int k_tiles, int n_tiles,
+                      float *__restrict__ c, int64_t ldc, int32_t *__restrict__ err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // stage data first (128-byte aligned), control block after it
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    Ctrl *ctrl = reinterpret_cast<Ctrl *>(smem + STAGES * STAGE_BYTES);
+    volatile uint32_t *abort_flag = &ctrl->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mi_n = (row_tiles + MT_R - 1) / MT_R;
+    const int mj_n = (n_tiles + MT_C - 1) / MT_C;
+    const int n_mt = mi_n * mj_n;
+    const int64_t cap = (int64_t)STEP_CAP_PER_K * k_tiles;
+    const int rows_total = row_tiles * TILE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&ctrl->full[s]), 1);
+            mbar_init(smem_u32(&ctrl->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
+            mbar_init(smem_u32(&ctrl->tmem_empty[b]), 128);
+        }
+        mbar_init(smem_u32(&ctrl->drain), 1);
+        ctrl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&ctrl->tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    if (warp >= 2) {
+        // clear both accumulators: every multiply accumulates
+        const uint32_t q = (uint32_t)(warp & 3);
+        for (uint32_t col = 0; col < TMEM_COLS; col += 32) tmem_st32_zero(tmem_base + ((q * 32u) << 16) + col);
+        tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        uint32_t slot = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ti < n_mt && ok; ti += gridDim.x) {
+            const int mt = order ? order[ti] : ti;
+            const int cnt = step_counts[mt];
+            if (cnt == 0) continue;
+            const int mi = mt / mj_n, mj = mt % mj_n;
+            const uint32_t *list = steps + (int64_t)mt * cap;
+            const uint8_t *a_base = half_a + (int64_t)mi * k_tiles * A_SLAB_BYTES;
+            const uint8_t *b_base = half_b + (int64_t)mj * B_SLAB_BYTES;
+            for (int i0 = 0; i0 < cnt && ok; i0 += 32) {
+                const uint32_t mine = (i0 + lane < cnt) ? __ldg(list + i0 + lane) : 0u;
+                const int nb = min(32, cnt - i0);
+                for (int j = 0; j < nb; j++) {
+                    const uint32_t w = __shfl_sync(0xffffffffu, mine, j);
+                    if (lane == 0) {
+                        const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
+                        ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, ERR_WAIT_EMPTY);
+                        if (ok) {
+                            const uint32_t k = step_k(w), rows = step_rows(w), cols = step_cols(w);
+                            const uint32_t bar = smem_u32(&ctrl->full[s]);
+                            const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
+                            const uint32_t b_dst = a_dst + A_SLAB_BYTES;
+                            ctrl->step_word[s] = w;
+                            mbar_arrive_expect_tx(bar, (__popc(rows) + __popc(cols)) * TILE_BYTES);
+                            const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
+                            if (rows == 0xfu) {
+                                bulk_g2s(a_dst, a_src, A_SLAB_BYTES, bar);
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < MT_R; q++)
+                                    if ((rows >> q) & 1u)
+                                        bulk_g2s(a_dst + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
+                            }
+                            const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
+                            uint32_t rest = cols;
+                            while (rest) {
+                                const int c0 = __ffs(rest) - 1;
+                                const uint32_t shifted = rest >> c0;
+                                const int len = __ffs(~shifted) - 1;   // run of ones starting at c0
+                                bulk_g2s(b_dst + c0 * TILE_BYTES, b_src + c0 * TILE_BYTES, len * TILE_BYTES, bar);
+                                rest &= ~(((1u << len) - 1u) << c0);
+                            }
+                            slot++;
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                }
+            }
+        }
+        if (lane == 0 && *abort_flag) {
+            // make sure every copy this block issued has landed before the block can exit
+            const uint32_t first = slot > STAGES ? slot - STAGES : 0;
+            for (uint32_t sl = first; sl < slot; sl++) {
+                const uint32_t s = sl % STAGES, ph = (sl / STAGES) & 1u;
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(smem_u32(&ctrl->full[s]), ph) && global_ns() - t0 < WAIT_LIMIT_NS) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ tensor-core issue
+        if (lane == 0) {
+            uint32_t slot = 0, acc_iter = 0;
+            bool ok = true;
+            for (int ti = blockIdx.x; ti < n_mt && ok; ti += gridDim.x) {
+                const int mt = order ? order[ti] : ti;
+                const int cnt = step_counts[mt];
+                if (cnt == 0) continue;
+                const uint32_t buf = acc_iter & 1u;
+                ok = wait_bounded(smem_u32(&ctrl->tmem_empty[buf]), ((acc_iter >> 1) & 1u) ^ 1u, abort_flag, err,
+                                  ERR_WAIT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int i = 0; i < cnt; i++) {
+                    const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
+                    ok = wait_bounded(smem_u32(&ctrl->full[s]), ph, abort_flag, err, ERR_WAIT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t w = ctrl->step_word[s];
+                    const uint32_t rows = step_rows(w), cols = step_cols(w);
+                    const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
+                    const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_SLAB_BYTES;
+                    uint32_t rest = cols;
+                    while (rest) {
+                        const int c0 = __ffs(rest) - 1;
+                        const uint32_t shifted = rest >> c0;
+                        const int len = __ffs(~shifted) - 1;
+                        const uint32_t n = (uint32_t)len * TILE;
+                        const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+                        const uint32_t d = tmem_base + buf * ACC_COLS + (uint32_t)c0 * TILE;
+#pragma unroll
+                        for (uint32_t ks = 0; ks < 2; ks++) {
+                            umma_f16(d, smem_desc(a_addr + ks * 256u),
+                                     smem_desc(b_addr + (uint32_t)c0 * TILE_BYTES + ks * 256u), idesc, m0, m1, m2, m3);
+                        }
+                        rest &= ~(((1u << len) - 1u) << c0);
+                    }
+                    umma_commit(smem_u32(&ctrl->empty[s]));
+                    slot++;
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+                acc_iter++;
+            }
+            if (*abort_flag) {
+                // wait for the multiplies already issued before tensor memory is freed
+                umma_commit(smem_u32(&ctrl->drain));
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(smem_u32(&ctrl->drain), 0) && global_ns() - t0 < WAIT_LIMIT_NS) {}
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps)
+        const uint32_t q = (uint32_t)(warp & 3);
+        const int e = threadIdx.x - 64;
+        uint32_t acc_iter = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ti < n_mt && ok; ti += gridDim.x) {
+            const int mt = order ? order[ti] : ti;
+            const int cnt = step_counts[mt];
+            const int mi = mt / mj_n, mj = mt % mj_n;
+            if (cnt == 0) {
+                const int col = mj * (MT_C * TILE) + (e & 63) * 4;
+                if (col < n_tiles * TILE) {
+                    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                    for (int rr = 0; rr < 64; rr++) {
+                        const int row = mi * (MT_R * TILE) + rr * 2 + (e >> 6);
+                        if (row < rows_total) __stcs(reinterpret_cast<float4 *>(c + (int64_t)row * ldc + col), z);
+                    }
+                }
+                continue;
+            }
+            const uint32_t buf = acc_iter & 1u;
+            ok = wait_bounded(smem_u32(&ctrl->tmem_full[buf]), (acc_iter >> 1) & 1u, abort_flag, err,
+                              ERR_WAIT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = mi * (MT_R * TILE) + (int)q * TILE + lane;
+            const bool row_ok = row < rows_total;
+            float *crow = c + (int64_t)row * ldc + (int64_t)mj * (MT_C * TILE);
+#pragma unroll 1
+            for (int cc = 0; cc < MT_C; cc++) {
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS + (uint32_t)cc * TILE;
+                uint32_t v[32];
+                tmem_ld32(taddr, v);
+                tmem_wait_ld();
+                tmem_st32_zero(taddr);
+                if (row_ok && mj * MT_C + cc < n_tiles) {
+#pragma unroll
+                    for (int x = 0; x < 8; x++) {
+                        float4 o;
+                        o.x = __uint_as_float(v[4 * x + 0]);
+                        o.y = __uint_as_float(v[4 * x + 1]);
+                        o.z = __uint_as_float(v[4 * x + 2]);
+                        o.w = __uint_as_float(v[4 * x + 3]);
+                        __stcs(reinterpret_cast<float4 *>(crow + cc * TILE + 4 * x), o);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+            acc_iter++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+}  // namespace spamm
+
+extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
+                                        const int32_t *d_step_counts, int row_tiles, int k_tiles, int n_tiles,
+                                        float *d_c, int64_t ldc, int32_t *d_error, void *stream)
+{
+    using namespace spamm;
+    if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_c || !d_error || row_tiles < 0 || k_tiles < 0 ||
+        n_tiles < 0 || ldc < (int64_t)n_tiles * TILE || (ldc & 3) || (reinterpret_cast<uintptr_t>(d_c) & 15) ||
+        (reinterpret_cast<uintptr_t>(d_half_a) & 15) || (reinterpret_cast<uintptr_t>(d_half_b) & 15))
+        return SPAMM_ERR_INVALID;
+    const int64_t n_mt = (int64_t)ceil_div(row_tiles, MT_R) * ceil_div(n_tiles, MT_C);
+    if (n_mt == 0) return SPAMM_OK;
+    if (n_mt > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+
+    static thread_local int configured_device = -1;
+    static thread_local int sm_count = 0;
+    int dev = 0;
+    SPAMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (configured_device != dev) {
+        cudaDeviceProp prop;
+        SPAMM_CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major != 10) return SPAMM_ERR_UNSUPPORTED;
+        SPAMM_CUDA_TRY(cudaFuncSetAttribute(gated_multiply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            GM_SMEM_BYTES));
+        sm_count = prop.multiProcessorCount;
+        configured_device = dev;
+    }
+    const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
+    gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, (cudaStream_t)stream>>>(
+        static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
+        nullptr, row_tiles, k_tiles, n_tiles, d_c, ldc, d_error);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}

@@ -1,0 +1,72 @@
+// Tile Frobenius-norm map: an HBM streaming kernel.
+//
+// Stands in for unroll_get_Fnorm_pri (reference cuSpAMM.cu:21-71) and, because the contract is float norms of
+// the float data, for unroll_get_Fnorm_FP16 (cuSpAMM.cu:74-123).  The reference runs one 128-thread block per
+// 2-4 KB tile; here one warp sweeps a strip of four adjacent tiles (32 rows x 128 columns = 16 KB) with one
+// 128-bit load per lane and row, so every row of the strip is one fully used 512-byte request, and the 32 loads
+// of a lane are independent of each other.
+//
+// Reduction order (the CPU checker uses the same, which makes the maps bit-equal):
+//   lane g (0..7) of a tile owns columns 4g..4g+3; rows 0..31 in order, the four columns left to right,
+//   acc = fma(x, x, acc) from +0; then acc_g + acc_{g^4}, then + the partner g^2, then + the partner g^1;
+//   norm = sqrt (round to nearest).  Additions of two partners are commutative, so all eight lanes hold the
+//   same bits after each step.
+#include "common.cuh"
+
+namespace spamm {
+
+__global__ void __launch_bounds__(256)
+norm_map_kernel(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld, float *__restrict__ map)
+{
+    const int lane = threadIdx.x & 31;
+    const int strips_per_row = (tile_cols + 3) >> 2;
+    const int64_t strip = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (strip >= (int64_t)tile_rows * strips_per_row) return;
+    const int tr = (int)(strip / strips_per_row);
+    const int ts = (int)(strip % strips_per_row);
+    const int col = ts * 128 + lane * 4;
+    const bool in_range = col < tile_cols * TILE;
+    const float *p = x + (int64_t)tr * TILE * ld + col;
+
+    float acc = 0.0f;
+#pragma unroll
+    for (int r0 = 0; r0 < TILE; r0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            v[r] = in_range ? __ldcs(reinterpret_cast<const float4 *>(p + (int64_t)(r0 + r) * ld))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            acc = __fmaf_rn(v[r].x, v[r].x, acc);
+            acc = __fmaf_rn(v[r].y, v[r].y, acc);
+            acc = __fmaf_rn(v[r].z, v[r].z, acc);
+            acc = __fmaf_rn(v[r].w, v[r].w, acc);
+        }
+    }
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+    if (in_range && (lane & 7) == 0) {
+        map[(int64_t)tr * tile_cols + ts * 4 + (lane >> 3)] = __fsqrt_rn(acc);
+    }
+}
+
+}  // namespace spamm
+
+extern "C" int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t ld, float *d_map, void *stream)
+{
+    using namespace spamm;
+    if (!d_x || !d_map || rows < 0 || cols < 0 || rows % TILE || cols % TILE || ld < cols || (ld & 3) ||
+        (reinterpret_cast<uintptr_t>(d_x) & 15))
+        return SPAMM_ERR_INVALID;
+    if (rows == 0 || cols == 0) return SPAMM_OK;
+    const int tile_rows = rows / TILE, tile_cols = cols / TILE;
+    const int64_t strips = (int64_t)tile_rows * ((tile_cols + 3) / 4);
+    const int64_t blocks = (strips + 7) / 8;
+    if (blocks > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+    norm_map_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(d_x, tile_rows, tile_cols, ld, d_map);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}

@@ -1,0 +1,544 @@
+// Host side of the C ABI: the plan object that replaces the reference's `main` (cuSpAMM.cu:395-556) --
+// configuration, per-device buffers, the timed loop body and its event timing.
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace spamm {
+
+static thread_local std::string g_last_cuda_error;
+
+int record_cuda_error(cudaError_t e, const char *what)
+{
+    g_last_cuda_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    if (e == cudaErrorMemoryAllocation) return SPAMM_ERR_ALLOC;
+    return SPAMM_ERR_CUDA;
+}
+
+// Scalars the kernels write; lives at the head of the buffer that is cleared before every list build.
+struct DeviceScalars {
+    unsigned long long survivors;
+    unsigned long long packed[2];
+    int32_t overflow;
+    int32_t error;
+};
+
+}  // namespace spamm
+
+using namespace spamm;
+
+struct spamm_plan {
+    int M = 0, K = 0, N = 0;
+    int row_begin = 0, row_tiles = 0;   // in tiles
+    int k_tiles = 0, n_tiles = 0, mi_n = 0, mj_n = 0;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    float *d_a = nullptr, *d_b = nullptr, *d_c = nullptr;
+    float *d_norm_a = nullptr, *d_norm_b = nullptr;
+    int32_t *d_counts = nullptr, *d_step_counts = nullptr;
+    uint32_t *d_steps = nullptr;
+    uint8_t *d_half_a = nullptr, *d_half_b = nullptr;
+    uint8_t *d_cleared = nullptr;       // [DeviceScalars | need_a | need_b], cleared per list build
+    size_t cleared_bytes = 0, need_a_off = 0, need_b_off = 0;
+    DeviceScalars *h_scalars = nullptr; // pinned
+    cudaEvent_t ev[8] = {};
+    bool have_norms = false, have_lists = false, have_pack = false;
+    int64_t launches = 0;
+
+    DeviceScalars *scalars() const { return reinterpret_cast<DeviceScalars *>(d_cleared); }
+    uint8_t *need_a() const { return d_cleared + need_a_off; }
+    uint8_t *need_b() const { return d_cleared + need_b_off; }
+    size_t bytes_a() const { return sizeof(float) * (size_t)row_tiles * TILE * K; }
+    size_t bytes_b() const { return sizeof(float) * (size_t)K * N; }
+    size_t bytes_c() const { return sizeof(float) * (size_t)row_tiles * TILE * N; }
+    size_t bytes_norm_a() const { return sizeof(float) * (size_t)row_tiles * k_tiles; }
+    size_t bytes_norm_b() const { return sizeof(float) * (size_t)k_tiles * n_tiles; }
+    size_t bytes_counts() const { return sizeof(int32_t) * (size_t)row_tiles * n_tiles; }
+    size_t n_mt() const { return (size_t)mi_n * mj_n; }
+    size_t step_cap() const { return (size_t)STEP_CAP_PER_K * k_tiles; }
+    size_t bytes_steps() const { return sizeof(uint32_t) * n_mt() * step_cap(); }
+    size_t bytes_step_counts() const { return sizeof(int32_t) * n_mt(); }
+    size_t bytes_half_a() const { return (size_t)mi_n * k_tiles * A_SLAB_BYTES; }
+    size_t bytes_half_b() const { return (size_t)k_tiles * mj_n * B_SLAB_BYTES; }
+};
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard()
+    {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+template <typename T>
+int dev_alloc(T **p, size_t bytes)
+{
+    *p = nullptr;
+    if (bytes == 0) bytes = 16;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(p), bytes);
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "cudaMalloc");
+        return SPAMM_ERR_ALLOC;
+    }
+    return SPAMM_OK;
+}
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int read_scalars(spamm_plan *p)
+{
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_scalars, p->scalars(), sizeof(DeviceScalars), cudaMemcpyDeviceToHost,
+                                   p->stream));
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    return SPAMM_OK;
+}
+
+int status_from_scalars(const spamm_plan *p)
+{
+    if (p->h_scalars->error) return SPAMM_ERR_DEVICE_WAIT;
+    if (p->h_scalars->overflow) return SPAMM_ERR_OVERFLOW;
+    return SPAMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin, int row_tile_count, int device)
+{
+    if (!out) return SPAMM_ERR_INVALID;
+    *out = nullptr;
+    if (M <= 0 || K <= 0 || N <= 0 || M % TILE || K % TILE || N % TILE) return SPAMM_ERR_INVALID;
+    if (row_tile_begin < 0 || row_tile_count < 0 || row_tile_begin + (int64_t)row_tile_count > M / TILE)
+        return SPAMM_ERR_INVALID;
+    if (K / TILE > 65535) return SPAMM_ERR_UNSUPPORTED;
+    int ndev = 0;
+    SPAMM_CUDA_TRY(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(device);
+    if (!guard.ok) return record_cuda_error(cudaGetLastError(), "cudaSetDevice");
+    cudaDeviceProp prop;
+    SPAMM_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return SPAMM_ERR_UNSUPPORTED;
+
+    spamm_plan *p = new (std::nothrow) spamm_plan();
+    if (!p) return SPAMM_ERR_ALLOC;
+    p->M = M; p->K = K; p->N = N;
+    p->row_begin = row_tile_begin; p->row_tiles = row_tile_count;
+    p->k_tiles = K / TILE; p->n_tiles = N / TILE;
+    p->mi_n = ceil_div(p->row_tiles, MT_R); p->mj_n = ceil_div(p->n_tiles, MT_C);
+    p->device = device;
+
+    int st = SPAMM_OK;
+    auto fail = [&](int code) {
+        spamm_plan_destroy(p);
+        return code;
+    };
+    if (cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess)
+        return fail(record_cuda_error(cudaGetLastError(), "cudaStreamCreate"));
+    for (auto &e : p->ev)
+        if (cudaEventCreate(&e) != cudaSuccess) return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
+    if ((st = dev_alloc(&p->d_a, p->bytes_a()))) return fail(st);
+    if ((st = dev_alloc(&p->d_b, p->bytes_b()))) return fail(st);
+    if ((st = dev_alloc(&p->d_c, p->bytes_c()))) return fail(st);
+    if ((st = dev_alloc(&p->d_norm_a, p->bytes_norm_a()))) return fail(st);
+    if ((st = dev_alloc(&p->d_norm_b, p->bytes_norm_b()))) return fail(st);
+    if ((st = dev_alloc(&p->d_counts, p->bytes_counts()))) return fail(st);
+    if ((st = dev_alloc(&p->d_step_counts, p->bytes_step_counts()))) return fail(st);
+    if ((st = dev_alloc(&p->d_steps, p->bytes_steps()))) return fail(st);
+    if ((st = dev_alloc(&p->d_half_a, p->bytes_half_a()))) return fail(st);
+    if ((st = dev_alloc(&p->d_half_b, p->bytes_half_b()))) return fail(st);
+    p->need_a_off = round_up(sizeof(DeviceScalars), 16);
+    p->need_b_off = p->need_a_off + round_up((size_t)p->mi_n * p->k_tiles, 16);
+    p->cleared_bytes = p->need_b_off + round_up((size_t)p->k_tiles * p->mj_n, 16);
+    if ((st = dev_alloc(&p->d_cleared, p->cleared_bytes))) return fail(st);
+    if (cudaMallocHost(reinterpret_cast<void **>(&p->h_scalars), sizeof(DeviceScalars)) != cudaSuccess)
+        return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
+    memset(p->h_scalars, 0, sizeof(DeviceScalars));
+    if (cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream) != cudaSuccess ||
+        cudaStreamSynchronize(p->stream) != cudaSuccess)
+        return fail(record_cuda_error(cudaGetLastError(), "cudaMemsetAsync"));
+    *out = p;
+    return SPAMM_OK;
+}
+
+int spamm_plan_destroy(spamm_plan *p)
+{
+    if (!p) return SPAMM_OK;
+    DeviceGuard guard(p->device);
+    if (p->stream) cudaStreamSynchronize(p->stream);
+    cudaFree(p->d_a); cudaFree(p->d_b); cudaFree(p->d_c);
+    cudaFree(p->d_norm_a); cudaFree(p->d_norm_b);
+    cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
+    cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared);
+    if (p->h_scalars) cudaFreeHost(p->h_scalars);
+    for (auto &e : p->ev)
+        if (e) cudaEventDestroy(e);
+    if (p->stream) cudaStreamDestroy(p->stream);
+    delete p;
+    return SPAMM_OK;
+}
+
+int spamm_upload(spamm_plan *p, const float *a_rows, const float *b)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    if (a_rows && p->row_tiles)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a, a_rows, p->bytes_a(), cudaMemcpyHostToDevice, p->stream));
+    if (b) SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream));
+    if (a_rows || b) p->have_norms = p->have_lists = p->have_pack = false;
+    return SPAMM_OK;
+}
+
+int spamm_norms_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
+{
+    if (!p || b_tile_begin < 0 || b_tile_count < 0 || b_tile_begin + (int64_t)b_tile_count > p->k_tiles)
+        return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    int st;
+    if (b_tile_count) {
+        st = spamm_norm_map_dev(p->d_b + (size_t)b_tile_begin * TILE * p->N, b_tile_count * TILE, p->N, p->N,
+                                p->d_norm_b + (size_t)b_tile_begin * p->n_tiles, p->stream);
+        if (st) return st;
+        p->launches++;
+    }
+    if (p->row_tiles) {
+        st = spamm_norm_map_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->stream);
+        if (st) return st;
+        p->launches++;
+    }
+    p->have_norms = true;
+    p->have_lists = p->have_pack = false;
+    return SPAMM_OK;
+}
+
+int spamm_norms(spamm_plan *p)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    return spamm_norms_share(p, 0, p->k_tiles);
+}
+
+int spamm_build_lists(spamm_plan *p, float tau)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    if (!p->have_norms) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
+    if (p->row_tiles) {
+        int st = spamm_build_lists_dev(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau, p->d_steps,
+                                       p->d_step_counts, p->d_counts, &p->scalars()->survivors, p->need_a(),
+                                       p->need_b(), &p->scalars()->overflow, p->stream);
+        if (st) return st;
+        p->launches++;
+    }
+    p->have_lists = true;
+    p->have_pack = false;
+    return SPAMM_OK;
+}
+
+int spamm_pack(spamm_plan *p)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    if (!p->have_lists) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    if (p->row_tiles) {
+        int st = spamm_pack_half_dev(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->need_a(), p->need_b(),
+                                     p->d_half_a, p->d_half_b, p->scalars()->packed, p->stream);
+        if (st) return st;
+        p->launches++;
+    }
+    p->have_pack = true;
+    return SPAMM_OK;
+}
+
+int spamm_gated_multiply(spamm_plan *p)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    if (!p->have_pack) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    if (p->row_tiles) {
+        int st = spamm_gated_multiply_dev(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->row_tiles,
+                                          p->k_tiles, p->n_tiles, p->d_c, p->N, &p->scalars()->error, p->stream);
+        if (st) return st;
+        p->launches++;
+    }
+    return SPAMM_OK;
+}
+
+int spamm_run(spamm_plan *p, float tau)
+{
+    int st;
+    if ((st = spamm_norms(p))) return st;
+    if ((st = spamm_build_lists(p, tau))) return st;
+    if ((st = spamm_pack(p))) return st;
+    return spamm_gated_multiply(p);
+}
+
+int spamm_sync(spamm_plan *p)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    int st = read_scalars(p);
+    if (st) return st;
+    return status_from_scalars(p);
+}
+
+int spamm_download_c(spamm_plan *p, float *c_rows)
+{
+    if (!p || !c_rows) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    if (p->row_tiles)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows, p->d_c, p->bytes_c(), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    return SPAMM_OK;
+}
+
+static void fill_stats(spamm_plan *p, spamm_stats *s)
+{
+    s->survivors = (int64_t)p->h_scalars->survivors;
+    s->tile_products = (int64_t)p->row_tiles * p->k_tiles * p->n_tiles;
+    s->packed_tiles_a = (int64_t)p->h_scalars->packed[0];
+    s->packed_tiles_b = (int64_t)p->h_scalars->packed[1];
+    s->executed_flops = 65536.0 * (double)s->survivors;
+}
+
+static int64_t sum_step_counts(spamm_plan *p, int *status)
+{
+    std::vector<int32_t> sc(p->n_mt());
+    *status = SPAMM_OK;
+    if (sc.empty()) return 0;
+    cudaError_t e = cudaMemcpyAsync(sc.data(), p->d_step_counts, p->bytes_step_counts(), cudaMemcpyDeviceToHost,
+                                    p->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(p->stream);
+    if (e != cudaSuccess) {
+        *status = record_cuda_error(e, "cudaMemcpyAsync(step counts)");
+        return 0;
+    }
+    int64_t t = 0;
+    for (int32_t v : sc) t += v;
+    return t;
+}
+
+// Records ev[0..4] around the four phases.
+static int run_with_events(spamm_plan *p, float tau)
+{
+    int st;
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[0], p->stream));
+    if ((st = spamm_norms(p))) return st;
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[1], p->stream));
+    if ((st = spamm_build_lists(p, tau))) return st;
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[2], p->stream));
+    if ((st = spamm_pack(p))) return st;
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[3], p->stream));
+    if ((st = spamm_gated_multiply(p))) return st;
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[4], p->stream));
+    return SPAMM_OK;
+}
+
+static int phase_times(spamm_plan *p, spamm_stats *s)
+{
+    SPAMM_CUDA_TRY(cudaEventElapsedTime(&s->ms_norm, p->ev[0], p->ev[1]));
+    SPAMM_CUDA_TRY(cudaEventElapsedTime(&s->ms_lists, p->ev[1], p->ev[2]));
+    SPAMM_CUDA_TRY(cudaEventElapsedTime(&s->ms_pack, p->ev[2], p->ev[3]));
+    SPAMM_CUDA_TRY(cudaEventElapsedTime(&s->ms_multiply, p->ev[3], p->ev[4]));
+    SPAMM_CUDA_TRY(cudaEventElapsedTime(&s->ms_device_total, p->ev[0], p->ev[4]));
+    return SPAMM_OK;
+}
+
+int spamm_run_timed(spamm_plan *p, float tau, spamm_stats *stats)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    int st = run_with_events(p, tau);
+    if (st) return st;
+    if ((st = read_scalars(p))) return st;
+    if (stats) {
+        memset(stats, 0, sizeof(*stats));
+        if ((st = phase_times(p, stats))) return st;
+        fill_stats(p, stats);
+        stats->steps = sum_step_counts(p, &st);
+        if (st) return st;
+    }
+    return status_from_scalars(p);
+}
+
+int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_rows, float tau, spamm_stats *stats)
+{
+    if (!p || !a_rows || !b || !c_rows) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    int st;
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
+    if ((st = spamm_upload(p, a_rows, b))) return st;
+    if ((st = run_with_events(p, tau))) return st;
+    if (p->row_tiles)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows, p->d_c, p->bytes_c(), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[6], p->stream));
+    if ((st = read_scalars(p))) return st;
+    if (stats) {
+        memset(stats, 0, sizeof(*stats));
+        if ((st = phase_times(p, stats))) return st;
+        SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
+        SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_d2h, p->ev[4], p->ev[6]));
+        fill_stats(p, stats);
+        stats->steps = sum_step_counts(p, &st);
+        if (st) return st;
+    }
+    return status_from_scalars(p);
+}
+
+int spamm_get_norm_a(spamm_plan *p, float *out)
+{
+    if (!p || !out) return SPAMM_ERR_INVALID;
+    if (!p->have_norms) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(out, p->d_norm_a, p->bytes_norm_a(), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    return SPAMM_OK;
+}
+
+int spamm_get_norm_b(spamm_plan *p, float *out)
+{
+    if (!p || !out) return SPAMM_ERR_INVALID;
+    if (!p->have_norms) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(out, p->d_norm_b, p->bytes_norm_b(), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    return SPAMM_OK;
+}
+
+int spamm_get_counts(spamm_plan *p, int32_t *out, int64_t *survivors)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    if (!p->have_lists) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    if (out && p->row_tiles)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(out, p->d_counts, p->bytes_counts(), cudaMemcpyDeviceToHost, p->stream));
+    int st = read_scalars(p);
+    if (st) return st;
+    if (survivors) *survivors = (int64_t)p->h_scalars->survivors;
+    return status_from_scalars(p);
+}
+
+int spamm_get_lists(spamm_plan *p, int64_t *offsets, int32_t *k_idx)
+{
+    if (!p || !offsets) return SPAMM_ERR_INVALID;
+    if (!p->have_lists) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    const size_t n_mt = p->n_mt();
+    const size_t tiles = (size_t)p->row_tiles * p->n_tiles;
+    std::vector<int32_t> sc(n_mt);
+    if (n_mt) {
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(sc.data(), p->d_step_counts, p->bytes_step_counts(), cudaMemcpyDeviceToHost,
+                                       p->stream));
+        SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    }
+    std::vector<size_t> first(n_mt + 1, 0);
+    for (size_t m = 0; m < n_mt; m++) first[m + 1] = first[m] + (size_t)sc[m];
+    std::vector<uint32_t> steps(first[n_mt]);
+    for (size_t m = 0; m < n_mt; m++) {
+        if (sc[m] > 0)
+            SPAMM_CUDA_TRY(cudaMemcpyAsync(steps.data() + first[m], p->d_steps + m * p->step_cap(),
+                                           sizeof(uint32_t) * (size_t)sc[m], cudaMemcpyDeviceToHost, p->stream));
+    }
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    // pass 1: list lengths
+    std::vector<int64_t> len(tiles, 0);
+    for (size_t m = 0; m < n_mt; m++) {
+        const int mi = (int)(m / p->mj_n), mj = (int)(m % p->mj_n);
+        for (size_t i = first[m]; i < first[m + 1]; i++) {
+            const uint32_t w = steps[i];
+            for (int r = 0; r < MT_R; r++) {
+                if (!((step_rows(w) >> r) & 1u)) continue;
+                for (int c = 0; c < MT_C; c++)
+                    if ((step_cols(w) >> c) & 1u) len[(size_t)(mi * MT_R + r) * p->n_tiles + (mj * MT_C + c)]++;
+            }
+        }
+    }
+    offsets[0] = 0;
+    for (size_t t = 0; t < tiles; t++) offsets[t + 1] = offsets[t] + len[t];
+    if (!k_idx) return SPAMM_OK;
+    std::vector<int64_t> cur(offsets, offsets + tiles);
+    for (size_t m = 0; m < n_mt; m++) {
+        const int mi = (int)(m / p->mj_n), mj = (int)(m % p->mj_n);
+        for (size_t i = first[m]; i < first[m + 1]; i++) {
+            const uint32_t w = steps[i];
+            for (int r = 0; r < MT_R; r++) {
+                if (!((step_rows(w) >> r) & 1u)) continue;
+                for (int c = 0; c < MT_C; c++)
+                    if ((step_cols(w) >> c) & 1u)
+                        k_idx[cur[(size_t)(mi * MT_R + r) * p->n_tiles + (mj * MT_C + c)]++] = (int32_t)step_k(w);
+            }
+        }
+    }
+    return SPAMM_OK;
+}
+
+int spamm_device_buffer(spamm_plan *p, int which, void **d_ptr, size_t *bytes)
+{
+    if (!p || !d_ptr || !bytes) return SPAMM_ERR_INVALID;
+    switch (which) {
+    case SPAMM_BUF_A: *d_ptr = p->d_a; *bytes = p->bytes_a(); break;
+    case SPAMM_BUF_B: *d_ptr = p->d_b; *bytes = p->bytes_b(); break;
+    case SPAMM_BUF_C: *d_ptr = p->d_c; *bytes = p->bytes_c(); break;
+    case SPAMM_BUF_NORM_A: *d_ptr = p->d_norm_a; *bytes = p->bytes_norm_a(); break;
+    case SPAMM_BUF_NORM_B: *d_ptr = p->d_norm_b; *bytes = p->bytes_norm_b(); break;
+    case SPAMM_BUF_COUNTS: *d_ptr = p->d_counts; *bytes = p->bytes_counts(); break;
+    case SPAMM_BUF_STEPS: *d_ptr = p->d_steps; *bytes = p->bytes_steps(); break;
+    case SPAMM_BUF_STEP_COUNTS: *d_ptr = p->d_step_counts; *bytes = p->bytes_step_counts(); break;
+    case SPAMM_BUF_HALF_A: *d_ptr = p->d_half_a; *bytes = p->bytes_half_a(); break;
+    case SPAMM_BUF_HALF_B: *d_ptr = p->d_half_b; *bytes = p->bytes_half_b(); break;
+    default: return SPAMM_ERR_INVALID;
+    }
+    return SPAMM_OK;
+}
+
+int spamm_stream(spamm_plan *p, void **stream)
+{
+    if (!p || !stream) return SPAMM_ERR_INVALID;
+    *stream = p->stream;
+    return SPAMM_OK;
+}
+
+int spamm_plan_dims(spamm_plan *p, int *M, int *K, int *N, int *row_tile_begin, int *row_tile_count)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    if (M) *M = p->M;
+    if (K) *K = p->K;
+    if (N) *N = p->N;
+    if (row_tile_begin) *row_tile_begin = p->row_begin;
+    if (row_tile_count) *row_tile_count = p->row_tiles;
+    return SPAMM_OK;
+}
+
+const char *spamm_status_string(int status)
+{
+    switch (status) {
+    case SPAMM_OK: return "ok";
+    case SPAMM_ERR_INVALID: return "invalid argument";
+    case SPAMM_ERR_CUDA: return "CUDA runtime error";
+    case SPAMM_ERR_ALLOC: return "allocation failed";
+    case SPAMM_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel ran out";
+    case SPAMM_ERR_STATE: return "call out of order";
+    case SPAMM_ERR_UNSUPPORTED: return "unsupported device or size";
+    case SPAMM_ERR_OVERFLOW: return "step list overflow";
+    default: return "unknown status";
+    }
+}
+
+const char *spamm_last_cuda_error(void) { return g_last_cuda_error.c_str(); }
+
+int64_t spamm_kernel_launches(spamm_plan *p) { return p ? p->launches : 0; }
+
+}  // extern "C"

@@ -1,0 +1,371 @@
+"""Host-side mirror of the reference driver (`main`, cuSpAMM.cu:395-556) on top of the C ABI.
+
+`SpammPlan` is one GPU working on one block of C tile rows -- the reference's per-device plan (`TGPUplan`,
+cuSpAMM.cu:6-12) with its row offset (cuSpAMM.cu:503,530).  `ShardedSpamm` is the multi-GPU split: one process
+per GPU, C sharded by row blocks, B and its norm map moved between the GPUs with NCCL (torch.distributed is used
+for the plumbing only), C slabs gathered on request.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _lib
+from ._lib import SpammStats, check
+
+TILE = 32
+MT_ROWS = 4
+MT_COLS = 8
+
+BUF_A, BUF_B, BUF_C, BUF_NORM_A, BUF_NORM_B, BUF_COUNTS, BUF_STEPS, BUF_STEP_COUNTS, BUF_HALF_A, BUF_HALF_B = range(10)
+
+
+def _host_ptr(x, nbytes: Optional[int] = None) -> int:
+    """Address of a contiguous float32 host array (numpy array or CPU torch tensor)."""
+    if x is None:
+        return 0
+    if isinstance(x, np.ndarray):
+        if x.dtype != np.float32 or not x.flags["C_CONTIGUOUS"]:
+            raise ValueError("host matrices must be C-contiguous float32")
+        if nbytes is not None and x.nbytes != nbytes:
+            raise ValueError(f"host matrix has {x.nbytes} bytes, expected {nbytes}")
+        return x.ctypes.data
+    if hasattr(x, "data_ptr"):  # torch tensor
+        import torch
+
+        if x.device.type != "cpu" or x.dtype != torch.float32 or not x.is_contiguous():
+            raise ValueError("host matrices must be contiguous float32 CPU tensors")
+        if nbytes is not None and x.numel() * 4 != nbytes:
+            raise ValueError(f"host matrix has {x.numel() * 4} bytes, expected {nbytes}")
+        return x.data_ptr()
+    raise TypeError("expected a numpy array or a CPU torch tensor")
+
+
+def row_blocks(row_tiles: int, world: int) -> list:
+    """Contiguous blocks of C tile rows, one per GPU, as the reference splits them (cuSpAMM.cu:503,530:
+    device d owns tile rows [d*T/G, (d+1)*T/G)).  Boundaries fall on multiples of 4 tile rows (one macro tile)
+    when there are enough rows, so that no GPU works on a partly filled macro tile; the remainder goes to the
+    first blocks.  Returns [(begin, count)] * world."""
+    if world <= 0 or row_tiles < 0:
+        raise ValueError("bad partition")
+    unit = MT_ROWS if row_tiles >= MT_ROWS * world else 1
+    units = row_tiles // unit
+    base, extra = divmod(units, world)
+    out, begin = [], 0
+    for r in range(world):
+        n = (base + (1 if r < extra else 0)) * unit
+        if r == world - 1:
+            n = row_tiles - begin
+        out.append((begin, n))
+        begin += n
+    return out
+
+
+class _DeviceView:
+    """Zero-copy view of plan-owned device memory for torch.as_tensor."""
+
+    def __init__(self, ptr: int, shape: Tuple[int, ...], typestr: str):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class SpammPlan:
+    """One GPU, one block of C tile rows.  Method names follow the steps of the reference's timed loop."""
+
+    def __init__(self, M: int, K: int, N: int, row_tile_begin: int = 0, row_tile_count: Optional[int] = None,
+                 device: int = 0):
+        self._lib = _lib.load()
+        if row_tile_count is None:
+            row_tile_count = M // TILE - row_tile_begin
+        self.M, self.K, self.N = M, K, N
+        self.row_tile_begin, self.row_tile_count = row_tile_begin, row_tile_count
+        self.device = device
+        self._h = C.c_void_p()
+        check(self._lib.spamm_plan_create(C.byref(self._h), M, K, N, row_tile_begin, row_tile_count, device),
+              "spamm_plan_create")
+
+    # ---- lifetime
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self._h.value:
+            self._lib.spamm_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ---- shapes
+    @property
+    def rows(self) -> int:
+        return self.row_tile_count * TILE
+
+    @property
+    def k_tiles(self) -> int:
+        return self.K // TILE
+
+    @property
+    def n_tiles(self) -> int:
+        return self.N // TILE
+
+    # ---- the driver steps
+    def upload(self, a_rows=None, b=None) -> None:
+        pa = _host_ptr(a_rows, self.rows * self.K * 4) if a_rows is not None else 0
+        pb = _host_ptr(b, self.K * self.N * 4) if b is not None else 0
+        check(self._lib.spamm_upload(self._h, pa, pb), "spamm_upload")
+
+    def norms(self) -> None:
+        check(self._lib.spamm_norms(self._h), "spamm_norms")
+
+    def norms_share(self, b_tile_begin: int, b_tile_count: int) -> None:
+        check(self._lib.spamm_norms_share(self._h, b_tile_begin, b_tile_count), "spamm_norms_share")
+
+    def build_lists(self, tau: float) -> None:
+        check(self._lib.spamm_build_lists(self._h, float(tau)), "spamm_build_lists")
+
+    def pack(self) -> None:
+        check(self._lib.spamm_pack(self._h), "spamm_pack")
+
+    def gated_multiply(self) -> None:
+        check(self._lib.spamm_gated_multiply(self._h), "spamm_gated_multiply")
+
+    def run(self, tau: float) -> None:
+        check(self._lib.spamm_run(self._h, float(tau)), "spamm_run")
+
+    def sync(self) -> None:
+        check(self._lib.spamm_sync(self._h), "spamm_sync")
+
+    def run_timed(self, tau: float) -> dict:
+        st = SpammStats()
+        check(self._lib.spamm_run_timed(self._h, float(tau), C.byref(st)), "spamm_run_timed")
+        return st.as_dict()
+
+    def download_c(self, out=None):
+        if out is None:
+            out = np.empty((self.rows, self.N), dtype=np.float32)
+        check(self._lib.spamm_download_c(self._h, _host_ptr(out, self.rows * self.N * 4)), "spamm_download_c")
+        return out
+
+    def multiply(self, a_rows, b, tau: float, out=None):
+        """Host matrices in, host matrix out (the whole loop body of the reference driver plus the copies)."""
+        if out is None:
+            out = np.empty((self.rows, self.N), dtype=np.float32)
+        st = SpammStats()
+        check(self._lib.spamm_multiply(self._h, _host_ptr(a_rows, self.rows * self.K * 4),
+                                       _host_ptr(b, self.K * self.N * 4), _host_ptr(out, self.rows * self.N * 4),
+                                       float(tau), C.byref(st)), "spamm_multiply")
+        return out, st.as_dict()
+
+    # ---- readbacks for the parity tests
+    def norm_a(self) -> np.ndarray:
+        out = np.empty((self.row_tile_count, self.k_tiles), dtype=np.float32)
+        check(self._lib.spamm_get_norm_a(self._h, out.ctypes.data), "spamm_get_norm_a")
+        return out
+
+    def norm_b(self) -> np.ndarray:
+        out = np.empty((self.k_tiles, self.n_tiles), dtype=np.float32)
+        check(self._lib.spamm_get_norm_b(self._h, out.ctypes.data), "spamm_get_norm_b")
+        return out
+
+    def counts(self) -> Tuple[np.ndarray, int]:
+        out = np.empty((self.row_tile_count, self.n_tiles), dtype=np.int32)
+        s = C.c_int64()
+        check(self._lib.spamm_get_counts(self._h, out.ctypes.data, C.byref(s)), "spamm_get_counts")
+        return out, int(s.value)
+
+    def lists(self) -> Tuple[np.ndarray, np.ndarray]:
+        """(offsets, k_idx): the per-C-tile skip lists the multiply kernel walks, in the reference's form."""
+        tiles = self.row_tile_count * self.n_tiles
+        offsets = np.zeros(tiles + 1, dtype=np.int64)
+        check(self._lib.spamm_get_lists(self._h, offsets.ctypes.data, None), "spamm_get_lists")
+        k_idx = np.empty(max(int(offsets[-1]), 1), dtype=np.int32)
+        check(self._lib.spamm_get_lists(self._h, offsets.ctypes.data, k_idx.ctypes.data), "spamm_get_lists")
+        return offsets, k_idx[: int(offsets[-1])]
+
+    def kernel_launches(self) -> int:
+        return int(self._lib.spamm_kernel_launches(self._h))
+
+    # ---- raw device memory, for moving data between GPUs
+    def buffer(self, which: int) -> Tuple[int, int]:
+        p, n = C.c_void_p(), C.c_size_t()
+        check(self._lib.spamm_device_buffer(self._h, which, C.byref(p), C.byref(n)), "spamm_device_buffer")
+        return int(p.value or 0), int(n.value)
+
+    @property
+    def stream_ptr(self) -> int:
+        s = C.c_void_p()
+        check(self._lib.spamm_stream(self._h, C.byref(s)), "spamm_stream")
+        return int(s.value or 0)
+
+    def as_tensor(self, which: int):
+        """torch view (no copy) of one of the plan's float/int32 device buffers."""
+        import torch
+
+        ptr, nbytes = self.buffer(which)
+        shapes = {
+            BUF_A: ((self.rows, self.K), "<f4"),
+            BUF_B: ((self.K, self.N), "<f4"),
+            BUF_C: ((self.rows, self.N), "<f4"),
+            BUF_NORM_A: ((self.row_tile_count, self.k_tiles), "<f4"),
+            BUF_NORM_B: ((self.k_tiles, self.n_tiles), "<f4"),
+            BUF_COUNTS: ((self.row_tile_count, self.n_tiles), "<i4"),
+        }
+        if which not in shapes:
+            raise ValueError("no tensor view for this buffer")
+        shape, typestr = shapes[which]
+        if 0 in shape:
+            dt = torch.float32 if typestr == "<f4" else torch.int32
+            return torch.empty(shape, dtype=dt, device=f"cuda:{self.device}")
+        return torch.as_tensor(_DeviceView(ptr, shape, typestr), device=f"cuda:{self.device}")
+
+    def torch_stream(self):
+        import torch
+
+        return torch.cuda.ExternalStream(self.stream_ptr, device=f"cuda:{self.device}")
+
+
+class ShardedSpamm:
+    """C sharded by row blocks over the ranks of a torch.distributed group (one process per GPU).
+
+    Mirrors the reference's multi-device loop (cuSpAMM.cu:433-451, 470-537) with two changes the reference's
+    own layout invites: B is uploaded once and broadcast over NVLink instead of one host copy per device
+    (cuSpAMM.cu:449-450), and every rank computes only its share of B's norm map, the shares being all-gathered,
+    instead of each device recomputing all of it (cuSpAMM.cu:486).
+
+    `plan_factory(M, K, N, begin, count)` builds the per-rank plan (default: a `SpammPlan` on the current CUDA
+    device); the tests pass a CPU stand-in to run the same orchestration over gloo.
+    """
+
+    def __init__(self, M: int, K: int, N: int, group=None, plan_factory=None, device: Optional[int] = None):
+        import torch
+        import torch.distributed as dist
+
+        self._torch, self._dist = torch, dist
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.M, self.K, self.N = M, K, N
+        self.blocks = row_blocks(M // TILE, self.world)
+        self.row_tile_begin, self.row_tile_count = self.blocks[self.rank]
+        if plan_factory is None:
+            dev = torch.cuda.current_device() if device is None else device
+            plan_factory = lambda M, K, N, b, c: SpammPlan(M, K, N, b, c, device=dev)  # noqa: E731
+        self.plan = plan_factory(M, K, N, self.row_tile_begin, self.row_tile_count)
+        k_tiles = K // TILE
+        # equal shares of B's tile rows when they divide evenly, otherwise every rank computes the whole map
+        self._share = (k_tiles // self.world) if (self.world > 1 and k_tiles % self.world == 0) else None
+
+    def _on_stream(self):
+        ts = getattr(self.plan, "torch_stream", None)
+        if ts is None:
+            import contextlib
+
+            return contextlib.nullcontext()
+        return self._torch.cuda.stream(ts())
+
+    def distribute(self, a_rows, b=None, src: int = 0) -> None:
+        """Every rank uploads its own rows of A; rank `src` uploads B, which is then broadcast to the others."""
+        self.plan.upload(a_rows, b if self.rank == src else None)
+        if self.world > 1:
+            with self._on_stream():
+                self._dist.broadcast(self.plan.as_tensor(BUF_B), src=src, group=self.group)
+
+    def run(self, tau: float) -> None:
+        """norm maps (B's shared between the ranks), lists, pack, multiply; asynchronous."""
+        if self._share is None:
+            self.plan.norms()
+        else:
+            self.plan.norms_share(self.rank * self._share, self._share)
+            with self._on_stream():
+                nb = self.plan.as_tensor(BUF_NORM_B)
+                mine = nb[self.rank * self._share:(self.rank + 1) * self._share]
+                if self._dist.get_backend(self.group) == "nccl":
+                    self._dist.all_gather_into_tensor(nb, mine, group=self.group)   # in place
+                else:
+                    parts = [nb[r * self._share:(r + 1) * self._share] for r in range(self.world)]
+                    self._dist.all_gather(parts, mine.clone(), group=self.group)
+        self.plan.build_lists(tau)
+        self.plan.pack()
+        self.plan.gated_multiply()
+
+    def sync(self) -> None:
+        self.plan.sync()
+
+    def survivors(self) -> int:
+        """S summed over all ranks."""
+        _, s = self.plan.counts()
+        if self.world == 1:
+            return s
+        dev = self.plan.as_tensor(BUF_NORM_B).device
+        t = self._torch.tensor([s], dtype=self._torch.int64, device=dev)
+        self._dist.all_reduce(t, group=self.group)
+        return int(t.item())
+
+    def gather_c(self, dst: int = 0):
+        """Gathers the C slabs on rank `dst` (device to device), returns the full C there as a tensor, else None."""
+        mine = self.plan.as_tensor(BUF_C)
+        if self.world == 1:
+            return mine
+        with self._on_stream():
+            if self.rank == dst:
+                full = self._torch.empty((self.M, self.N), dtype=mine.dtype, device=mine.device)
+                parts = [full[b * TILE:(b + n) * TILE] for b, n in self.blocks]
+            else:
+                full, parts = None, None
+            self._dist.gather(mine, parts, dst=dst, group=self.group)
+        self.plan.sync()
+        return full
+
+    def close(self) -> None:
+        close = getattr(self.plan, "close", None)
+        if close:
+            close()
+
+
+# ---- generators (host side) -------------------------------------------------------------------------------
+
+def _gen(fn_name: str, rows: int, cols: int, *args) -> np.ndarray:
+    lib = _lib.load()
+    out = np.empty((rows, cols), dtype=np.float32)
+    check(getattr(lib, fn_name)(out.ctypes.data, *args), fn_name)
+    return out
+
+
+def gen_decay_exp(c: float, v: float, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
+    """a_ij = c * v^|i-j| (getDecayMatrixExp, tool.cu:409-422)."""
+    return _gen("spamm_gen_decay_exp", rows, cols, c, v, row_begin, rows, cols)
+
+
+def gen_decay_alg(c: float, v: float, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
+    """a_ij = c / (|i-j|^v + 1) (getDecayMatrixAlg, tool.cu:426-436)."""
+    return _gen("spamm_gen_decay_alg", rows, cols, c, v, row_begin, rows, cols)
+
+
+def gen_signed_exp(lam: float, seed: int, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
+    """a_ij = s_ij * exp(-lam*|i-j|), s_ij = +-1 from a hash of (seed, i, j)."""
+    return _gen("spamm_gen_signed_exp", rows, cols, lam, seed, row_begin, rows, cols)
+
+
+def gen_uniform_alg(seed: int, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
+    """a_ij = u_ij / (|i-j|^2 + 1), u uniform in [-1, 1)."""
+    return _gen("spamm_gen_uniform_alg", rows, cols, seed, row_begin, rows, cols)
+
+
+def gen_uniform(seed: int, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
+    """a_ij uniform in [-1, 1)."""
+    return _gen("spamm_gen_uniform", rows, cols, seed, row_begin, rows, cols)
+
+
+def gen_lattice(L: int, seed: int, rows: Optional[int] = None, row_begin: int = 0) -> np.ndarray:
+    """Symmetric surrogate of a density matrix on an L^3 grid: a_ij = +-u * exp(-|r_i - r_j|), u in [0.5, 1)."""
+    n = L ** 3
+    rows = n - row_begin if rows is None else rows
+    return _gen("spamm_gen_lattice", rows, n, L, seed, row_begin, rows)

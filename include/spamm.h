@@ -1,0 +1,232 @@
+/*
+ * spamm.h -- C ABI of libspamm.so, a B200 (sm_100a) engine for SpAMM
+ * (Sparse Approximate Matrix Multiply) over 32x32 tiles:
+ *
+ *      C(i,j) = sum over k with  ||A(i,k)||_F * ||B(k,j)||_F >= tau  of  half(A(i,k)) * half(B(k,j))
+ *
+ * The reference benchmark (buaa-hipo/cuSpAMM) has no library interface: its boundary is a set of
+ * compile-time constants plus four kernel launches issued by `main`.  Each entry point below names the
+ * reference lines it stands in for (paths inside the reference project).
+ *
+ * Conventions
+ *   - all matrices are row-major float; M, K, N must be multiples of 32 (the reference pads to that,
+ *     main.h:54-56; callers pad with zeros);
+ *   - a plan owns one GPU and one block of C tile rows [row_tile_begin, row_tile_begin+row_tile_count),
+ *     which is the reference's per-device row split (cuSpAMM.cu:503,530 `main_row_offset`); one plan per
+ *     process and GPU, a multi-GPU run is several plans;
+ *   - every function returns a spamm_status (0 = success); nothing prints, exits or throws;
+ *   - pointers named d_* are device pointers of the plan's GPU, all others are host pointers;
+ *   - a plan is not thread-safe; calls on one plan are ordered on the plan's CUDA stream.
+ */
+#ifndef SPAMM_H
+#define SPAMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPAMM_TILE 32          /* LoNum, main.h:32 */
+#define SPAMM_MT_ROWS 4        /* C tiles per macro tile, vertically (128 rows)  */
+#define SPAMM_MT_COLS 8        /* C tiles per macro tile, horizontally (256 columns) */
+
+typedef enum spamm_status {
+    SPAMM_OK = 0,
+    SPAMM_ERR_INVALID = 1,      /* bad argument (null pointer, dimension not a multiple of 32, bad row block) */
+    SPAMM_ERR_CUDA = 2,         /* a CUDA runtime call failed; see spamm_last_cuda_error */
+    SPAMM_ERR_ALLOC = 3,        /* device or host allocation failed */
+    SPAMM_ERR_DEVICE_WAIT = 4,  /* a bounded wait inside a kernel ran out; results are not valid */
+    SPAMM_ERR_STATE = 5,        /* call out of order (e.g. multiply before build_lists) */
+    SPAMM_ERR_UNSUPPORTED = 6,  /* not an sm_100 GPU, or a size beyond a documented limit */
+    SPAMM_ERR_OVERFLOW = 7      /* a per-macro-tile step list did not fit (needs non-finite norms) */
+} spamm_status;
+
+typedef struct spamm_plan spamm_plan;
+
+/* Per-call figures; times are CUDA-event milliseconds on the plan's stream. */
+typedef struct spamm_stats {
+    float ms_h2d;               /* host->device copies of A rows and B (spamm_multiply only) */
+    float ms_norm;              /* both norm maps */
+    float ms_lists;             /* skip-list build */
+    float ms_pack;              /* float->half packing of the tiles some list names */
+    float ms_multiply;          /* gated multiply, including writing every C tile */
+    float ms_d2h;               /* device->host copy of the C rows (spamm_multiply only) */
+    float ms_device_total;      /* norm + lists + pack + multiply, one event pair around all four */
+    int64_t survivors;          /* S: tile products executed (== sum of the per-tile list lengths) */
+    int64_t tile_products;      /* row_tile_count * (K/32) * (N/32) */
+    int64_t steps;              /* entries of the macro-tile step lists the multiply kernel walked */
+    int64_t packed_tiles_a;     /* A tiles converted to half this call */
+    int64_t packed_tiles_b;     /* B tiles converted to half this call */
+    double executed_flops;      /* 65536 * S */
+} spamm_stats;
+
+/* Names for spamm_device_buffer. */
+typedef enum spamm_buffer {
+    SPAMM_BUF_A = 0,            /* float  [row_tile_count*32][K]   this plan's rows of A                      */
+    SPAMM_BUF_B = 1,            /* float  [K][N]                                                               */
+    SPAMM_BUF_C = 2,            /* float  [row_tile_count*32][N]   this plan's rows of C                      */
+    SPAMM_BUF_NORM_A = 3,       /* float  [row_tile_count][K/32]                                               */
+    SPAMM_BUF_NORM_B = 4,       /* float  [K/32][N/32]                                                         */
+    SPAMM_BUF_COUNTS = 5,       /* int32  [row_tile_count][N/32]   list length of every C tile                 */
+    SPAMM_BUF_STEPS = 6,        /* uint32 [macro tiles][step capacity]                                         */
+    SPAMM_BUF_STEP_COUNTS = 7,  /* int32  [macro tiles]                                                        */
+    SPAMM_BUF_HALF_A = 8,       /* packed half tiles of A (2 KiB each, see spamm_pack_half_dev)                */
+    SPAMM_BUF_HALF_B = 9        /* packed half tiles of B                                                      */
+} spamm_buffer;
+
+/* ---------------------------------------------------------------- plan: the reference's `main` ---- */
+
+/*
+ * Replaces the compile-time configuration and per-device allocation of the reference:
+ * inM/inK/inN (para.h:6-8), the row split over DEVICEDIM devices (para.h:9, cuSpAMM.cu:503,530) and
+ * the cudaMallocManaged block (cuSpAMM.cu:433-451).  `device` is a CUDA ordinal.  Allocates every device
+ * buffer the path needs; no later call allocates.
+ */
+int spamm_plan_create(spamm_plan **out, int M, int K, int N,
+                      int row_tile_begin, int row_tile_count, int device);
+int spamm_plan_destroy(spamm_plan *plan);
+
+/*
+ * Host->device copies (cuSpAMM.cu:449-450).  a_rows points at the FIRST ROW OF THIS PLAN'S BLOCK
+ * (row_tile_begin*32 of the full matrix), leading dimension K; b is the whole of B.  Either may be NULL
+ * to leave that operand as it is.  Asynchronous on the plan's stream when the host memory is pinned.
+ */
+int spamm_upload(spamm_plan *plan, const float *a_rows, const float *b);
+
+/*
+ * The timed region of the reference (cuSpAMM.cu:458-546) in four steps, all asynchronous on the plan's
+ * stream.  spamm_run issues the four in order.
+ *   spamm_norms        both norm maps            (unroll_get_Fnorm_*, launches at cuSpAMM.cu:486,503)
+ *   spamm_build_lists  skip lists for tau        (cuSpAMM.cu:302-334; tau is the float `Norm`, compared with >=)
+ *   spamm_pack         half copies of the tiles that some list names (the reference converts every
+ *                      element on the host at generation time, tool.cu:418)
+ *   spamm_gated_multiply   C rows of this plan   (get_C_FP16_B32, cuSpAMM.cu:336-391)
+ */
+int spamm_norms(spamm_plan *plan);
+int spamm_build_lists(spamm_plan *plan, float tau);
+int spamm_pack(spamm_plan *plan);
+int spamm_gated_multiply(spamm_plan *plan);
+int spamm_run(spamm_plan *plan, float tau);
+
+/*
+ * spamm_norms with only tile rows [b_tile_begin, b_tile_begin+b_tile_count) of B's norm map computed here; the
+ * caller fills the rest of SPAMM_BUF_NORM_B (e.g. an all-gather between the GPUs that each computed a share)
+ * before spamm_build_lists.  The reference recomputes the whole map of B on every device (cuSpAMM.cu:486).
+ */
+int spamm_norms_share(spamm_plan *plan, int b_tile_begin, int b_tile_count);
+
+/* Waits for the plan's stream, then reports a device-side wait that ran out (SPAMM_ERR_DEVICE_WAIT) or SPAMM_OK. */
+int spamm_sync(spamm_plan *plan);
+
+/* Device->host copy of this plan's C rows (leading dimension N) into c_rows; blocking. */
+int spamm_download_c(spamm_plan *plan, float *c_rows);
+
+/*
+ * One call for the whole driver loop body with host matrices in and out (north-star surface:
+ * "fp32 host matrices in and out"): upload, norms, lists, pack, multiply, download; blocking.
+ * a_rows / c_rows are this plan's row block, b is all of B.  stats may be NULL.
+ */
+int spamm_multiply(spamm_plan *plan, const float *a_rows, const float *b, float *c_rows,
+                   float tau, spamm_stats *stats);
+
+/* Same as spamm_run but records per-phase events; blocking.  Inputs must already be resident. */
+int spamm_run_timed(spamm_plan *plan, float tau, spamm_stats *stats);
+
+/* Readbacks used by the parity tests (blocking).  Sizes as in spamm_buffer. */
+int spamm_get_norm_a(spamm_plan *plan, float *out);
+int spamm_get_norm_b(spamm_plan *plan, float *out);
+int spamm_get_counts(spamm_plan *plan, int32_t *out, int64_t *survivors);
+/*
+ * The skip lists the multiply kernel actually walks, expanded to the per-C-tile form of the reference
+ * (sC_offset, cuSpAMM.cu:315-326): offsets has row_tile_count*(N/32)+1 entries, k_idx[offsets[t]..offsets[t+1])
+ * are the surviving k of tile t (row-major tile order inside this plan's block), ascending.
+ * Call once with k_idx == NULL to learn offsets (and the total in offsets[last]).
+ */
+int spamm_get_lists(spamm_plan *plan, int64_t *offsets, int32_t *k_idx);
+
+/* Raw access for callers that move data between GPUs themselves (NCCL broadcast of B and of its norm map). */
+int spamm_device_buffer(spamm_plan *plan, int which, void **d_ptr, size_t *bytes);
+/* The plan's cudaStream_t, as an opaque pointer. */
+int spamm_stream(spamm_plan *plan, void **stream);
+int spamm_plan_dims(spamm_plan *plan, int *M, int *K, int *N, int *row_tile_begin, int *row_tile_count);
+
+/* ---------------------------------------------------------------- kernels on caller memory -------- */
+/* `stream` is a cudaStream_t passed as void*; all launches are asynchronous. */
+
+/*
+ * Frobenius-norm map of a row-major float matrix (rows x cols, leading dimension ld elements):
+ * d_map[(r/32)*(cols/32) + c/32] = sqrt(sum of squares of the tile).  Replaces unroll_get_Fnorm_pri
+ * (cuSpAMM.cu:21-71) and, as the contract is float norms of float data, unroll_get_Fnorm_FP16 (cuSpAMM.cu:74-123).
+ * d_x must be 16-byte aligned and ld a multiple of 4.
+ */
+int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t ld, float *d_map, void *stream);
+
+/*
+ * Skip-list build (cuSpAMM.cu:302-334) for row_tiles x (N/32) C tiles.  For every macro tile of
+ * SPAMM_MT_ROWS x SPAMM_MT_COLS C tiles it writes a list of steps, ascending in k; a step is
+ *     bits 0-15  k,   bits 16-19  which of the 4 tile rows take part,   bits 20-27  which of the 8 tile columns,
+ * and every (row, column) pair of a step is a surviving product, every surviving product is in exactly one step.
+ * d_steps holds step_capacity (= 8*(K/32)) words per macro tile, macro tiles in row-major order.
+ * d_counts[row_tiles][N/32] receives the per-tile list lengths, *d_survivors their sum.
+ * d_need_a / d_need_b (one byte per A slab of 4 tiles / B slab of 8 tiles; must be zero on entry) receive the
+ * tiles that appear in some list.  d_overflow is set non-zero if a list did not fit.
+ */
+int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,
+                          float tau, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
+                          unsigned long long *d_survivors, uint8_t *d_need_a, uint8_t *d_need_b,
+                          int32_t *d_overflow, void *stream);
+
+/*
+ * float -> half (round to nearest even, as __float2half at tool.cu:418) of the flagged 32x32 tiles into the
+ * packed layout the multiply kernel loads: every tile is 2 KiB,
+ *     byte offset of element (o, kk) = (o/8)*512 + (kk/8)*128 + (o%8)*16 + (kk%8)*2,
+ * o = row of an A tile / column of a B tile, kk = the index that is summed over.  A tiles are grouped
+ * 4 (rows) to a slab, slabs ordered [row group][k]; B tiles 8 (columns) to a slab, slabs ordered [k][column group].
+ */
+int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
+                        const uint8_t *d_need_a, const uint8_t *d_need_b, void *d_half_a, void *d_half_b,
+                        unsigned long long *d_packed_tiles, void *stream);
+
+/*
+ * Gated multiply (get_C_FP16_B32, cuSpAMM.cu:336-391): walks the step lists, multiplies on the tensor cores
+ * (half inputs, float accumulation) and writes every C tile of the block, zeros where a list is empty.
+ * d_error (one int32, zero on entry) is set non-zero if a bounded device wait ran out.
+ */
+int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
+                             const int32_t *d_step_counts, int row_tiles, int k_tiles, int n_tiles,
+                             float *d_c, int64_t ldc, int32_t *d_error, void *stream);
+
+/* ---------------------------------------------------------------- generators and misc ------------- */
+
+/*
+ * Input generators of the reference (host side, float out):
+ *   spamm_gen_decay_exp  a_ij = c * v^|i-j|          (getDecayMatrixExp, tool.cu:409-422)
+ *   spamm_gen_decay_alg  a_ij = c / (|i-j|^v + 1)    (getDecayMatrixAlg, tool.cu:426-436)
+ * and seeded variants used by the benchmark configurations (sign or magnitude drawn from a counter-based
+ * hash of (seed, i, j), so any block of rows can be generated independently):
+ *   spamm_gen_signed_exp    a_ij = s_ij * exp(-lambda*|i-j|),  s_ij = +-1
+ *   spamm_gen_uniform_alg   a_ij = u_ij / (|i-j|^2 + 1),       u_ij uniform in [-1,1)
+ *   spamm_gen_uniform       a_ij = u_ij,                       u_ij uniform in [-1,1)
+ *   spamm_gen_lattice       a_ij = u * exp(-|r_i - r_j|), points on an L^3 cubic grid in lexicographic order,
+ *                           u uniform in [0.5,1) with a random sign, symmetric (hash of (min(i,j), max(i,j)))
+ * Rows [row_begin, row_begin+rows) of an (.. x cols) matrix are written to `out` (leading dimension cols).
+ */
+int spamm_gen_decay_exp(float *out, float c, float v, int64_t row_begin, int64_t rows, int64_t cols);
+int spamm_gen_decay_alg(float *out, float c, float v, int64_t row_begin, int64_t rows, int64_t cols);
+int spamm_gen_signed_exp(float *out, double lambda, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols);
+int spamm_gen_uniform_alg(float *out, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols);
+int spamm_gen_uniform(float *out, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols);
+int spamm_gen_lattice(float *out, int L, uint64_t seed, int64_t row_begin, int64_t rows);
+
+const char *spamm_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char *spamm_last_cuda_error(void);
+/* Launches counted since the plan was created (kernels of this library only). */
+int64_t spamm_kernel_launches(spamm_plan *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPAMM_H */

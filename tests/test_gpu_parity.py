@@ -1,0 +1,92 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker on the same seeded inputs.
+
+Bars: norm maps bit-equal; skip lists (lengths and k indices) bit-equal; C within relative Frobenius error 1e-3
+of the checker (the tolerance the target states for half inputs; observed values are ~1e-6, the difference being
+only the order of the float accumulation inside the tensor cores).
+"""
+import numpy as np
+import pytest
+
+from conftest import rel_fro, signed_decay
+
+pytestmark = pytest.mark.gpu
+
+C_TOL = 1e-3
+
+
+def run_plan(A, B, tau, row_begin=0, row_count=None):
+    from cuspamm_b200 import SpammPlan
+
+    M, K = A.shape
+    N = B.shape[1]
+    with SpammPlan(M, K, N, row_begin, row_count) as p:
+        p.upload(np.ascontiguousarray(A[p.row_tile_begin * 32:(p.row_tile_begin + p.row_tile_count) * 32]), B)
+        p.run(tau)
+        p.sync()
+        out = dict(C=p.download_c(), nA=p.norm_a(), nB=p.norm_b())
+        out["counts"], out["S"] = p.counts()
+        out["offsets"], out["kidx"] = p.lists()
+    return out
+
+
+def check_against_oracle(oracle, A, B, tau, row_begin=0, row_count=None):
+    got = run_plan(A, B, tau, row_begin, row_count)
+    Cref, S, nA, nB, counts = oracle.spamm(A, B, tau, row_begin, row_count, want_maps=True)
+    assert np.array_equal(got["nA"].view(np.uint32), nA.view(np.uint32)), "norm map of A differs"
+    assert np.array_equal(got["nB"].view(np.uint32), nB.view(np.uint32)), "norm map of B differs"
+    assert got["S"] == S
+    assert np.array_equal(got["counts"], counts)
+    full_nA = oracle.norm_map(A)
+    _, offs, kidx = oracle.lists(full_nA, nB, tau, row_begin, counts.shape[0])
+    assert np.array_equal(got["offsets"], offs)
+    assert np.array_equal(got["kidx"], kidx)
+    err = rel_fro(got["C"], Cref)
+    assert err <= C_TOL, f"C rel-Frobenius error {err}"
+    # tiles whose list is empty are exact zeros
+    empty = counts == 0
+    if empty.any():
+        Ct = got["C"].reshape(counts.shape[0], 32, counts.shape[1], 32)
+        assert not Ct.transpose(0, 2, 1, 3)[empty].any()
+    return got, err
+
+
+@pytest.mark.parametrize("n", [32, 64, 96, 128])
+def test_tiny_elementwise(oracle, n):
+    A = signed_decay(n, 0.3, seed=n)
+    B = signed_decay(n, 0.2, seed=n + 1)
+    got, _ = check_against_oracle(oracle, A, B, 1e-3)
+    Cref, _ = oracle.spamm(A, B, 1e-3)
+    np.testing.assert_allclose(got["C"], Cref, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("tau", [0.0, 1e-6, 1e-2, 0.5, 5.0, 1e9])
+def test_partial_masks_256(oracle, tau):
+    A = signed_decay(256, 0.05, seed=7)
+    B = signed_decay(256, 0.08, seed=8)
+    check_against_oracle(oracle, A, B, tau)
+
+
+def test_rectangular(oracle):
+    rng = np.random.default_rng(3)
+    A = (rng.standard_normal((160, 96)) * np.exp(-rng.random((160, 96)) * 6)).astype(np.float32)
+    B = (rng.standard_normal((96, 416)) * np.exp(-rng.random((96, 416)) * 6)).astype(np.float32)
+    check_against_oracle(oracle, A, B, 0.6)
+
+
+def test_config1_n1024(oracle):
+    """BASELINE config 1: N=1024, A=B, a_ij = +-exp(-0.5|i-j|), tau=1e-6."""
+    from cuspamm_b200 import gen_signed_exp
+
+    A = gen_signed_exp(0.5, 1, 1024, 1024)
+    got, err = check_against_oracle(oracle, A, A.copy(), 1e-6)
+    assert 0 < got["S"] < 32 ** 3
+    assert err < 1e-4
+
+
+def test_row_block(oracle):
+    A = signed_decay(512, 0.02, seed=11)
+    B = signed_decay(512, 0.03, seed=12)
+    full, _ = check_against_oracle(oracle, A, B, 0.05)
+    part, _ = check_against_oracle(oracle, A, B, 0.05, row_begin=5, row_count=7)
+    assert rel_fro(part["C"], full["C"][5 * 32:12 * 32]) < 1e-6
+    assert np.array_equal(part["counts"], full["counts"][5:12])
