@@ -1,5 +1,6 @@
 // Host side of the C ABI: the plan object that replaces the reference's `main` (cuSpAMM.cu:395-556) --
 // configuration, per-device buffers, the timed loop body and its event timing.
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -45,6 +46,10 @@ struct spamm_plan {
     uint8_t *d_cleared = nullptr;       // [DeviceScalars | need_a | need_b], cleared per list build
     size_t cleared_bytes = 0, need_a_off = 0, need_b_off = 0;
     DeviceScalars *h_scalars = nullptr; // pinned
+    void *d_cv_scratch = nullptr;       // partial sums of the valid-product counter
+    size_t cv_scratch_bytes = 0;
+    unsigned long long *d_cv_count = nullptr;   // [count, sum(double)] on the device
+    unsigned long long *h_cv = nullptr;         // pinned mirror of the two
     cudaEvent_t ev[8] = {};
     bool have_norms = false, have_lists = false, have_pack = false;
     int64_t launches = 0;
@@ -164,7 +169,12 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     p->need_b_off = p->need_a_off + round_up((size_t)p->mi_n * p->k_tiles, 16);
     p->cleared_bytes = p->need_b_off + round_up((size_t)p->k_tiles * p->mj_n, 16);
     if ((st = dev_alloc(&p->d_cleared, p->cleared_bytes))) return fail(st);
+    p->cv_scratch_bytes = spamm_count_valid_scratch_bytes(p->row_tiles, p->n_tiles);
+    if ((st = dev_alloc(&p->d_cv_scratch, p->cv_scratch_bytes))) return fail(st);
+    if ((st = dev_alloc(&p->d_cv_count, 16))) return fail(st);
     if (cudaMallocHost(reinterpret_cast<void **>(&p->h_scalars), sizeof(DeviceScalars)) != cudaSuccess)
+        return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
+    if (cudaMallocHost(reinterpret_cast<void **>(&p->h_cv), 16) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
     memset(p->h_scalars, 0, sizeof(DeviceScalars));
     if (cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream) != cudaSuccess ||
@@ -183,7 +193,9 @@ int spamm_plan_destroy(spamm_plan *p)
     cudaFree(p->d_norm_a); cudaFree(p->d_norm_b);
     cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
     cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared);
+    cudaFree(p->d_cv_scratch); cudaFree(p->d_cv_count);
     if (p->h_scalars) cudaFreeHost(p->h_scalars);
+    if (p->h_cv) cudaFreeHost(p->h_cv);
     for (auto &e : p->ev)
         if (e) cudaEventDestroy(e);
     if (p->stream) cudaStreamDestroy(p->stream);
@@ -482,6 +494,66 @@ int spamm_get_lists(spamm_plan *p, int64_t *offsets, int32_t *k_idx)
             }
         }
     }
+    return SPAMM_OK;
+}
+
+int spamm_count_valid(spamm_plan *p, float tau, int64_t *count, double *sum_of_products)
+{
+    if (!p || !count) return SPAMM_ERR_INVALID;
+    if (!p->have_norms) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    int st = spamm_count_valid_dev(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
+                                   p->d_cv_scratch, p->cv_scratch_bytes, p->d_cv_count,
+                                   reinterpret_cast<double *>(p->d_cv_count + 1), p->stream);
+    if (st) return st;
+    p->launches += 2;
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_cv, p->d_cv_count, 16, cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    *count = (int64_t)p->h_cv[0];
+    if (sum_of_products) memcpy(sum_of_products, &p->h_cv[1], sizeof(double));
+    return SPAMM_OK;
+}
+
+// smallest float that is >= x: "float product >= x" in double is the same test as "float product >= this"
+static float float_at_least(double x)
+{
+    float f = (float)x;
+    if ((double)f < x) f = nextafterf(f, INFINITY);
+    return f;
+}
+
+int spamm_tune_tau(spamm_plan *p, double expected_rate, int max_iters, double tolerance, float *tau, double *rate,
+                   int *iters)
+{
+    if (!p || !tau || max_iters <= 0 || !(tolerance > 0)) return SPAMM_ERR_INVALID;
+    if (!p->have_norms) return SPAMM_ERR_STATE;
+    const double total = (double)p->row_tiles * p->k_tiles * p->n_tiles;
+    double norm = 0.0, up = 0.0, down = 0.0, valid_rate = 0.0;
+    int it = 0;
+    for (; it < max_iters; it++) {
+        int64_t count = 0;
+        double ave = 0.0;
+        int st = spamm_count_valid(p, float_at_least(norm), &count, &ave);
+        if (st) return st;
+        valid_rate = total > 0 ? (double)((float)count / (float)total) : 0.0;
+        if (fabs(valid_rate - expected_rate) < tolerance) break;
+        if (it == 0) {
+            norm = total > 0 ? ave / total : 0.0;
+            up = norm;
+            continue;
+        }
+        if (valid_rate > expected_rate) {
+            if (up == norm) up *= 2;
+            down = norm;
+            norm = (norm + up) / 2;
+        } else {
+            up = norm;
+            norm = (norm + down) / 2;
+        }
+    }
+    *tau = (float)norm;
+    if (rate) *rate = valid_rate;
+    if (iters) *iters = it;
     return SPAMM_OK;
 }
 

@@ -190,6 +190,19 @@ class SpammPlan:
         check(self._lib.spamm_get_lists(self._h, offsets.ctypes.data, k_idx.ctypes.data), "spamm_get_lists")
         return offsets, k_idx[: int(offsets[-1])]
 
+    def count_valid(self, tau: float) -> Tuple[int, float]:
+        """(count, sum of norm products): countValid of the reference (tool.cu:493-529) on the GPU."""
+        c, s = C.c_int64(), C.c_double()
+        check(self._lib.spamm_count_valid(self._h, float(tau), C.byref(c), C.byref(s)), "spamm_count_valid")
+        return int(c.value), float(s.value)
+
+    def tune_tau(self, expected_rate: float = 0.75, max_iters: int = 20, tolerance: float = 0.01):
+        """(tau, rate, iterations): tuneValidRate of the reference (tool.cu:438-490, main.h:35-38)."""
+        tau, rate, it = C.c_float(), C.c_double(), C.c_int()
+        check(self._lib.spamm_tune_tau(self._h, expected_rate, max_iters, tolerance, C.byref(tau), C.byref(rate),
+                                       C.byref(it)), "spamm_tune_tau")
+        return float(tau.value), float(rate.value), int(it.value)
+
     def kernel_launches(self) -> int:
         return int(self._lib.spamm_kernel_launches(self._h))
 
@@ -314,13 +327,24 @@ class ShardedSpamm:
         mine = self.plan.as_tensor(BUF_C)
         if self.world == 1:
             return mine
+        equal = len({n for _, n in self.blocks}) == 1
         with self._on_stream():
             if self.rank == dst:
                 full = self._torch.empty((self.M, self.N), dtype=mine.dtype, device=mine.device)
                 parts = [full[b * TILE:(b + n) * TILE] for b, n in self.blocks]
             else:
                 full, parts = None, None
-            self._dist.gather(mine, parts, dst=dst, group=self.group)
+            if equal:
+                self._dist.gather(mine, parts, dst=dst, group=self.group)
+            elif self.rank == dst:
+                # slabs of different heights: one receive per peer
+                parts[dst].copy_(mine)
+                reqs = [self._dist.irecv(parts[r], src=r, group=self.group)
+                        for r in range(self.world) if r != dst and parts[r].numel()]
+                for q in reqs:
+                    q.wait()
+            elif mine.numel():
+                self._dist.send(mine, dst=dst, group=self.group)
         self.plan.sync()
         return full
 

@@ -146,6 +146,20 @@ int spamm_get_counts(spamm_plan *plan, int32_t *out, int64_t *survivors);
  */
 int spamm_get_lists(spamm_plan *plan, int64_t *offsets, int32_t *k_idx);
 
+/*
+ * Number of tile products of this plan's block whose norm product is >= tau, and the sum of all norm products:
+ * the reference's countValid (tool.cu:493-529) as two kernels over the norm maps.  Needs spamm_norms; blocking.
+ */
+int spamm_count_valid(spamm_plan *plan, float tau, int64_t *count, double *sum_of_products);
+/*
+ * Threshold for a wanted valid ratio: the reference's tuneValidRate (tool.cu:438-490) -- first guess the mean norm
+ * product, then bisection until |ratio - expected_rate| < tolerance or max_iters passes (ExpectedRate 0.75,
+ * TUNINGERROR 0.01, TUNINGTIME 20 in main.h:35-38) -- with every count done on the GPU.  Needs spamm_norms; blocking.
+ * *tau is the value to pass to spamm_build_lists; *rate the ratio of the last count; *iters the passes used.
+ */
+int spamm_tune_tau(spamm_plan *plan, double expected_rate, int max_iters, double tolerance, float *tau,
+                   double *rate, int *iters);
+
 /* Raw access for callers that move data between GPUs themselves (NCCL broadcast of B and of its norm map). */
 int spamm_device_buffer(spamm_plan *plan, int which, void **d_ptr, size_t *bytes);
 /* The plan's cudaStream_t, as an opaque pointer. */
@@ -197,6 +211,16 @@ int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k
 int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                              const int32_t *d_step_counts, int row_tiles, int k_tiles, int n_tiles,
                              float *d_c, int64_t ldc, int32_t *d_error, void *stream);
+
+/*
+ * countValid (tool.cu:493-529) on caller memory: *d_count = #{(i,k,j): nA(i,k)*nB(k,j) >= tau}, *d_sum (may be
+ * NULL) = the sum of all products in double.  d_scratch is work space of at least
+ * spamm_count_valid_scratch_bytes(row_tiles, n_tiles) bytes, 16-byte aligned; its contents are overwritten.
+ */
+size_t spamm_count_valid_scratch_bytes(int row_tiles, int n_tiles);
+int spamm_count_valid_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,
+                          float tau, void *d_scratch, size_t scratch_bytes, unsigned long long *d_count,
+                          double *d_sum, void *stream);
 
 /* ---------------------------------------------------------------- generators and misc ------------- */
 

@@ -40,6 +40,9 @@ def lib() -> C.CDLL:
         L.oracle_spamm.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp, vp, vp]
         L.oracle_gen_decay_exp.restype, L.oracle_gen_decay_exp.argtypes = None, [vp, f, f, i, i]
         L.oracle_gen_decay_alg.restype, L.oracle_gen_decay_alg.argtypes = None, [vp, f, f, i, i]
+        L.oracle_tune_valid_rate.restype = f
+        L.oracle_tune_valid_rate.argtypes = [vp, vp, i, i, i, C.c_double, i, C.c_double, C.POINTER(C.c_double),
+                                             C.POINTER(i)]
         L.oracle_num_threads.restype, L.oracle_num_threads.argtypes = i, []
         L.oracle_set_num_threads.restype, L.oracle_set_num_threads.argtypes = None, [i]
         _lib = L
@@ -113,6 +116,15 @@ def spamm(A, B, tau: float, row_begin: int = 0, row_count=None, want_maps: bool 
     if S < 0:
         raise ValueError("oracle_spamm rejected the arguments")
     return (Cm, int(S), nA, nB, counts) if want_maps else (Cm, int(S))
+
+
+def tune_valid_rate(nA, nB, expected: float = 0.75, max_iters: int = 20, tolerance: float = 0.01):
+    """(tau, rate, iterations) of the reference's bisection tuner."""
+    nA, nB = _f32(nA), _f32(nB)
+    rate, it = C.c_double(), C.c_int()
+    tau = lib().oracle_tune_valid_rate(nA.ctypes.data, nB.ctypes.data, nA.shape[0], nB.shape[0], nB.shape[1],
+                                       expected, max_iters, tolerance, C.byref(rate), C.byref(it))
+    return float(tau), float(rate.value), int(it.value)
 
 
 def gen_decay_exp(c: float, v: float, m: int, n: int) -> np.ndarray:

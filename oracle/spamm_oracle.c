@@ -297,6 +297,53 @@ done:
     return S;
 }
 
+/* ------------------------------------------------------- threshold tuner */
+
+/*
+ * tuneValidRate, tool.cu:438-490 (constants main.h:35-38): count the products >= Norm and sum all products
+ * (the float product widened to double, tool.cu:457-459); stop when |rate - expected| < tolerance; the first
+ * pass sets Norm to the mean product, later passes bisect.  rate is (float)count/total as at tool.cu:468.
+ * Returns (float)Norm; *rate_out and *iters_out report the last pass.
+ */
+float oracle_tune_valid_rate(const float *nA, const float *nB, int TM, int TK, int TN,
+                             double expected, int max_iters, double tolerance,
+                             double *rate_out, int *iters_out)
+{
+    double Norm = 0, up = 0, down = 0, validRate = 0;
+    double total = (double)TM * TK * TN;
+    int Ti;
+    for (Ti = 0; Ti < max_iters; Ti++) {
+        int64_t count = 0;
+        double ave = 0;
+        for (int i = 0; i < TM; i++)
+            for (int j = 0; j < TN; j++)
+                for (int k = 0; k < TK; k++) {
+                    volatile float prod = nA[(int64_t)i * TK + k] * nB[(int64_t)k * TN + j];
+                    double norm = prod;
+                    ave += norm;
+                    if (norm >= Norm) count++;
+                }
+        validRate = total > 0 ? (double)((float)count / (float)total) : 0.0;
+        if (fabs(validRate - expected) < tolerance) break;
+        if (Ti == 0) {
+            Norm = total > 0 ? ave / total : 0.0;
+            up = Norm;
+            continue;
+        }
+        if (validRate > expected) {
+            if (up == Norm) up *= 2;
+            down = Norm;
+            Norm = (Norm + up) / 2;
+        } else {
+            up = Norm;
+            Norm = (Norm + down) / 2;
+        }
+    }
+    if (rate_out) *rate_out = validRate;
+    if (iters_out) *iters_out = Ti;
+    return (float)Norm;
+}
+
 /* ------------------------------------------------------------ generators */
 
 /* tool.cu:409-422: a_ij = c * v^|i-j|, evaluated as (float)pow(v, |i-j|) with v a float. */

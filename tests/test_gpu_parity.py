@@ -90,3 +90,26 @@ def test_row_block(oracle):
     part, _ = check_against_oracle(oracle, A, B, 0.05, row_begin=5, row_count=7)
     assert rel_fro(part["C"], full["C"][5 * 32:12 * 32]) < 1e-6
     assert np.array_equal(part["counts"], full["counts"][5:12])
+
+
+def test_count_valid_and_tuner(oracle):
+    """countValid / tuneValidRate of the reference (tool.cu:438-529) on the GPU against the CPU restatement."""
+    from cuspamm_b200 import SpammPlan, gen_decay_alg
+
+    n = 1024
+    A = gen_decay_alg(0.1, 0.1, n, n)          # the reference's default generator (cuSpAMM.cu:428-431)
+    B = gen_decay_alg(0.1, 0.1, n, n)
+    nA, nB = oracle.norm_map(A), oracle.norm_map(B)
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        p.norms()
+        for tau in [0.0, 0.5, 1.548969, 2.0, 100.0]:
+            cnt, s = p.count_valid(tau)
+            prod = nA[:, :, None] * nB[None, :, :]
+            assert cnt == int((prod >= np.float32(tau)).sum())
+            assert abs(s - prod.astype(np.float64).sum()) <= 1e-9 * abs(s)
+        tau_g, rate_g, it_g = p.tune_tau(0.75, 20, 0.01)
+    tau_o, rate_o, it_o = oracle.tune_valid_rate(nA, nB, 0.75, 20, 0.01)
+    assert it_g == it_o
+    assert rate_g == rate_o
+    assert abs(tau_g - tau_o) <= 1e-6 * abs(tau_o)
