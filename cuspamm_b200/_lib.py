@@ -62,6 +62,8 @@ SIGNATURES = {
     "spamm_tune_tau": (_i, [_vp, C.c_double, _i, C.c_double, C.POINTER(_f), C.POINTER(C.c_double), C.POINTER(_i)]),
     "spamm_count_valid_scratch_bytes": (_sz, [_i, _i]),
     "spamm_count_valid_dev": (_i, [_vp, _vp, _i, _i, _i, _f, _vp, _sz, _vp, _vp, _vp]),
+    "spamm_count_valid_static": (_i, [_vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp]),
+    "spamm_count_valid_static_max_blocks": (_i, []),
     "spamm_device_buffer": (_i, [_vp, _i, _pp, C.POINTER(_sz)]),
     "spamm_stream": (_i, [_vp, _pp]),
     "spamm_plan_dims": (_i, [_vp] + [C.POINTER(_i)] * 5),

@@ -27,6 +27,7 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Records a CUDA error for spamm_last_cuda_error and maps it to a status.
 int record_cuda_error(cudaError_t e, const char *what);
+void record_error_text(const char *text);
 
 #define SPAMM_CUDA_TRY(call)                                                    \
     do {                                                                        \

@@ -7,6 +7,8 @@
 // map, broadcast reads of A's), and the block writes ONE partial count and ONE partial sum of products to a
 // scratch array; a second, single-block kernel adds the partials in index order, so the result does not depend
 // on scheduling.
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace spamm {
@@ -128,4 +130,74 @@ extern "C" int spamm_count_valid_dev(const float *d_norm_a, const float *d_norm_
         return SPAMM_ERR_INVALID;
     return launch_count_valid(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau,
                               static_cast<CountPartial *>(d_scratch), d_count, d_sum, (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// The same count for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc when they need a count: a process whose framework has already
+// taken all of HBM into its own caching pool, so that a raw allocation fails or fragments the pool; a serving loop
+// that must not stall, since cudaMalloc and cudaFree synchronise the whole device; a plugin that is handed its
+// buffers by its host and is forbidden to create more.  They still own the inputs (the two norm maps) and the
+// outputs (the count and the sum); what they cannot supply is the work space for the per-block partial sums.  That
+// work space lives here, in device memory that is part of the loaded library image: one fixed array per GPU, held
+// from the moment the library is loaded on that GPU until the process exits.
+namespace spamm {
+
+constexpr int CV_STATIC_MAX_BLOCKS = 8192;   // 8192 partials x 16 B = 128 KiB per GPU
+
+static __device__ __align__(256) unsigned char g_count_valid_scratch[CV_STATIC_MAX_BLOCKS * sizeof(CountPartial)];
+
+// Device address of the array above, per CUDA device.  In host code the array's name is only a handle of the
+// runtime, not an address a kernel can use, so the address is asked for once per device with that device current.
+constexpr int CV_MAX_DEVICES = 64;
+static CountPartial *g_cv_scratch_addr[CV_MAX_DEVICES] = {};
+
+static int static_scratch_for_current_device(CountPartial **out)
+{
+    int dev = 0;
+    SPAMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= CV_MAX_DEVICES) {
+        record_error_text("spamm_count_valid_static: device ordinal beyond 63");
+        return SPAMM_ERR_UNSUPPORTED;
+    }
+    if (!g_cv_scratch_addr[dev]) {
+        void *ptr = nullptr;
+        SPAMM_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_count_valid_scratch));
+        if (!ptr) {
+            record_error_text("spamm_count_valid_static: the scratch array has no device address");
+            return SPAMM_ERR_CUDA;
+        }
+        g_cv_scratch_addr[dev] = static_cast<CountPartial *>(ptr);
+    }
+    *out = g_cv_scratch_addr[dev];
+    return SPAMM_OK;
+}
+
+}  // namespace spamm
+
+extern "C" int spamm_count_valid_static_max_blocks(void) { return CV_STATIC_MAX_BLOCKS; }
+
+extern "C" int spamm_count_valid_static(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles,
+                                        int n_tiles, float tau, unsigned long long *d_count, double *d_sum,
+                                        void *stream)
+{
+    if (!d_norm_a || !d_norm_b || !d_count || row_tiles < 0 || k_tiles < 0 || n_tiles < 0) return SPAMM_ERR_INVALID;
+    const int64_t blocks = count_valid_blocks(row_tiles, n_tiles);
+    if (blocks > CV_STATIC_MAX_BLOCKS) {
+        static thread_local char msg[160];
+        snprintf(msg, sizeof(msg),
+                 "spamm_count_valid_static: %lld partial sums needed (row_tiles * ceil(n_tiles/256)), the built-in "
+                 "array holds %d; use spamm_count_valid_dev with caller scratch",
+                 (long long)blocks, CV_STATIC_MAX_BLOCKS);
+        record_error_text(msg);
+        return SPAMM_ERR_UNSUPPORTED;
+    }
+    CountPartial *scratch = nullptr;
+    int st = static_scratch_for_current_device(&scratch);
+    if (st) return st;
+    // Nothing in the array has to start at zero: every block of the first kernel overwrites its own slot and the
+    // second kernel reads only the slots written by this call.
+    return launch_count_valid(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, scratch, d_count, d_sum,
+                              (cudaStream_t)stream);
 }

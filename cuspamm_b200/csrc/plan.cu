@@ -20,6 +20,9 @@ int record_cuda_error(cudaError_t e, const char *what)
     return SPAMM_ERR_CUDA;
 }
 
+// Stores a detail message for spamm_last_cuda_error when the failing call is not a CUDA runtime call.
+void record_error_text(const char *text) { g_last_cuda_error = text; }
+
 // Scalars the kernels write; lives at the head of the buffer that is cleared before every list build.
 struct DeviceScalars {
     unsigned long long survivors;

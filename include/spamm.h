@@ -222,6 +222,24 @@ int spamm_count_valid_dev(const float *d_norm_a, const float *d_norm_b, int row_
                           float tau, void *d_scratch, size_t scratch_bytes, unsigned long long *d_count,
                           double *d_sum, void *stream);
 
+/*
+ * spamm_count_valid_dev without caller scratch and without any allocation.  No counterpart in the reference: it
+ * exists for hosts that cannot call cudaMalloc at this point (all of HBM already sits in their framework's own
+ * pool; a serving loop that must not hit the device-wide synchronisation of cudaMalloc/cudaFree; a plugin that
+ * may only use the buffers it is handed).  The caller still passes the norm maps and the two outputs; the
+ * per-block partial sums go to a fixed 128 KiB array inside the library image, which every GPU that loads the
+ * library holds until the process exits.
+ * Limit: row_tiles * ceil(n_tiles/256) <= spamm_count_valid_static_max_blocks() (8192; a square N=32768 problem
+ * needs 4096).  Larger problems are refused with SPAMM_ERR_UNSUPPORTED and a message in spamm_last_cuda_error.
+ * The first call on a GPU looks up the array's device address (with that GPU current); make that first call
+ * outside any stream capture.  All calls on one GPU share the array and it keeps the previous call's contents
+ * (nothing in it needs clearing): two calls that overlap on the GPU -- different streams, or different host
+ * threads -- race on it and must be ordered by the caller.
+ */
+int spamm_count_valid_static(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,
+                             float tau, unsigned long long *d_count, double *d_sum, void *stream);
+int spamm_count_valid_static_max_blocks(void);
+
 /* ---------------------------------------------------------------- generators and misc ------------- */
 
 /*
