@@ -157,6 +157,7 @@ def run_reference_arm(args):
         return
     from oracle import oracle as O
 
+    O.set_num_threads(os.cpu_count() or 1)     # torchrun exports OMP_NUM_THREADS=1; this arm owns the host cores
     n, tau = args.n, args.tau
     A = np.empty((n, n), dtype=np.float32)
     B = np.empty((n, n), dtype=np.float32)
@@ -342,6 +343,7 @@ def run_ours(args):
         try:
             from oracle import oracle as O
 
+            O.set_num_threads(os.cpu_count() or 1)
             A = np.ascontiguousarray(a_np)
             B = np.ascontiguousarray(b_np)
             Ah, Bh = O.round_to_half(A), O.round_to_half(B)

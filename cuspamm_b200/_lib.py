@@ -68,9 +68,11 @@ SIGNATURES = {
     "spamm_stream": (_i, [_vp, _pp]),
     "spamm_plan_dims": (_i, [_vp] + [C.POINTER(_i)] * 5),
     "spamm_norm_map_dev": (_i, [_vp, _i, _i, _i64, _vp, _vp]),
-    "spamm_build_lists_dev": (_i, [_vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "spamm_pack_half_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "spamm_gated_multiply_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i64, _vp, _vp]),
+    "spamm_build_lists_scratch_bytes": (_sz, [_i, _i, _i]),
+    "spamm_build_lists_dev": (_i, [_vp, _vp, _i, _i, _i, _f] + [_vp] * 10),
+    "spamm_pack_half_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "spamm_gated_multiply_dev": (_i, [_vp] * 7 + [_i, _i, _i, _vp, _i64, _vp]),
+    "spamm_macro_tile_order": (_i, [_i, _i, _vp]),
     "spamm_gen_decay_exp": (_i, [_vp, _f, _f, _i64, _i64, _i64]),
     "spamm_gen_decay_alg": (_i, [_vp, _f, _f, _i64, _i64, _i64]),
     "spamm_gen_signed_exp": (_i, [_vp, C.c_double, C.c_uint64, _i64, _i64, _i64]),

@@ -5,11 +5,15 @@
 // (cuSpAMM.cu:300,391).  The reference runs one 128-thread block per 32x32 C tile with 16x16x16 WMMA fragments.
 // Here a persistent block per SM walks macro tiles of 128 x 256 C elements (4 x 8 tiles):
 //
-//   warp 0      producer: reads the macro tile's step list and issues bulk copies (cp.async.bulk, completion on
+//   warp 0      scheduler + producer: claims macro tiles from a device-wide work counter (those with steps first),
+//               publishes them to the other warps through a small ring, reads the macro tile's step list and
+//               issues bulk copies (cp.async.bulk, completion on
 //               an mbarrier) of the packed half tiles a step names into a ring of shared-memory stages;
 //   warp 1      one elected thread issues tcgen05.mma (M=128, N=32*run, K=16) per run of adjacent tile columns
 //               of a step; the step's row set becomes the instruction's disable-output-lane mask, so tile rows
 //               that did not survive are not touched -- no product outside the lists is ever added;
+//   warps 6-9   fillers: when few macro tiles have steps, write the all-zero macro tiles from the start, in
+//               parallel with the pipeline;
 //   warps 2-5   epilogue: read the 128x256 float accumulator from tensor memory (tcgen05.ld), store it to C,
 //               clear it for the next macro tile; macro tiles without any step are written as zeros directly.
 //
@@ -22,11 +26,12 @@ namespace spamm {
 
 constexpr int STAGES = 6;
 constexpr int STAGE_BYTES = A_SLAB_BYTES + B_SLAB_BYTES;   // 24 KiB
-constexpr int GM_THREADS = 192;
+constexpr int GM_THREADS = 320;                            // producer, MMA, 4 epilogue warps, 4 filler warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = MT_C * TILE;                  // 256
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
-constexpr int SMEM_CTRL_BYTES = 256;
+constexpr int SMEM_CTRL_BYTES = 384;
+constexpr int SCHED = 4;                                    // depth of the ring of scheduled macro tiles
 constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 128;
 
 struct Ctrl {
@@ -35,6 +40,12 @@ struct Ctrl {
     unsigned long long tmem_full[2];
     unsigned long long tmem_empty[2];
     unsigned long long drain;
+    unsigned long long sched_full[SCHED];
+    unsigned long long sched_empty[SCHED];
+    int32_t filler_claim[2][4];
+    uint32_t filler_base[2];
+    int32_t tile_slot[SCHED];
+    int32_t tile_cnt[SCHED];
     uint32_t step_word[STAGES];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -155,24 +166,45 @@ __device__ __forceinline__ void tmem_st32_zero(uint32_t taddr)
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_TMEM_EMPTY = 3, ERR_WAIT_TMEM_FULL = 4, ERR_WAIT_DRAIN = 5 };
+// Writes one macro tile of C as zeros with `nthreads` threads (a multiple of 64); `t` is the caller's index among them.
+__device__ __forceinline__ void zero_fill_macro_tile(float *__restrict__ c, int64_t ldc, int mi, int mj, int rows_total,
+                                                     int cols_total, int t, int nthreads)
+{
+    const int col = mj * (MT_C * TILE) + (t & 63) * 4;
+    if (col >= cols_total) return;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int rows_per_pass = nthreads >> 6;
+    const int row0 = mi * (MT_R * TILE) + (t >> 6);
+#pragma unroll 4
+    for (int rr = 0; rr < MT_R * TILE; rr += rows_per_pass) {
+        const int row = row0 + rr;
+        if (row < rows_total) __stcs(reinterpret_cast<float4 *>(c + (int64_t)row * ldc + col), z);
+    }
+}
+
+enum {
+    ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_TMEM_EMPTY = 3, ERR_WAIT_TMEM_FULL = 4, ERR_WAIT_DRAIN = 5,
+    ERR_WAIT_SCHED_EMPTY = 6, ERR_WAIT_SCHED_FULL = 7
+};
 
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restrict__ half_b,
                       const uint32_t *__restrict__ steps, const int32_t *__restrict__ step_counts,
-                      const int32_t *__restrict__ order, int row_tiles, int k_tiles, int n_tiles,
-                      float *__restrict__ c, int64_t ldc, int32_t *__restrict__ err)
+                      const int32_t *__restrict__ order, const int32_t *__restrict__ busy_list,
+                      spamm_list_scalars *__restrict__ sc, int row_tiles, int k_tiles, int n_tiles,
+                      float *__restrict__ c, int64_t ldc)
 {
     extern __shared__ uint8_t smem_raw[];
     // stage data first (128-byte aligned), control block after it
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     Ctrl *ctrl = reinterpret_cast<Ctrl *>(smem + STAGES * STAGE_BYTES);
     volatile uint32_t *abort_flag = &ctrl->abort_flag;
+    int32_t *err = &sc->error;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mi_n = (row_tiles + MT_R - 1) / MT_R;
     const int mj_n = (n_tiles + MT_C - 1) / MT_C;
-    const int n_mt = mi_n * mj_n;
+    const unsigned int n_mt = (unsigned int)(mi_n * mj_n);
     const int64_t cap = (int64_t)STEP_CAP_PER_K * k_tiles;
     const int rows_total = row_tiles * TILE;
 
@@ -184,6 +216,10 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         for (int b = 0; b < 2; b++) {
             mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
             mbar_init(smem_u32(&ctrl->tmem_empty[b]), 128);
+        }
+        for (int d = 0; d < SCHED; d++) {
+            mbar_init(smem_u32(&ctrl->sched_full[d]), 1);
+            mbar_init(smem_u32(&ctrl->sched_empty[d]), 5);   // the MMA thread + one lane of each epilogue warp
         }
         mbar_init(smem_u32(&ctrl->drain), 1);
         ctrl->abort_flag = 0;
@@ -212,19 +248,79 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
     tc_fence_after();
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        uint32_t slot = 0;
+        // ------------------------------------------------------------------ scheduler + producer
+        // Work queue: macro tiles that have steps come first (they take several times longer than a macro tile
+        // that is only written as zeros, so starting them first keeps the tail short), then all others in the
+        // given order.  When most macro tiles have steps the first phase is skipped and the given order, which is
+        // chosen for operand reuse in L2, is used for everything.
+        const unsigned int busy_n = sc->busy_count;
+        const bool use_busy = busy_n * 4u <= n_mt;
+        const unsigned int chunk = use_busy ? 4u : 1u;     // zero-only macro tiles are claimed four at a time
+        int phase = use_busy ? 1 : 2;
+        int cand_mt = -1, cand_cnt = 0;                    // per lane: candidates of the claimed chunk
+        uint32_t pending = 0;                              // lanes whose candidate is still to be scheduled
+        uint32_t slot = 0, sidx = 0;
         bool ok = true;
-        for (int ti = blockIdx.x; ti < n_mt && ok; ti += gridDim.x) {
-            const int mt = order ? order[ti] : ti;
-            const int cnt = step_counts[mt];
+        while (ok) {
+            int mt = -1, cnt = 0;
+            if (phase == 1) {
+                unsigned int ti = 0;
+                if (lane == 0) ti = atomicAdd(&sc->queue_busy, 1u);
+                ti = __shfl_sync(0xffffffffu, ti, 0);
+                if (ti >= busy_n) {
+                    phase = 2;
+                    continue;
+                }
+                mt = busy_list[ti];
+                cnt = step_counts[mt];
+            } else {
+                bool exhausted = false;
+                while (!pending && !exhausted) {
+                    unsigned int p0 = 0;
+                    if (lane == 0) p0 = atomicAdd(&sc->queue_all, chunk);
+                    p0 = __shfl_sync(0xffffffffu, p0, 0);
+                    if (p0 >= n_mt) {
+                        exhausted = true;
+                        break;
+                    }
+                    cand_mt = -1;
+                    if ((unsigned int)lane < chunk && p0 + lane < n_mt) {
+                        cand_mt = order ? order[p0 + lane] : (int)(p0 + lane);
+                        cand_cnt = step_counts[cand_mt];
+                        if (use_busy && cand_cnt > 0) cand_mt = -1;     // already handled in the first phase
+                    }
+                    pending = __ballot_sync(0xffffffffu, cand_mt >= 0);
+                }
+                if (!exhausted) {
+                    const int src = __ffs(pending) - 1;
+                    pending &= pending - 1;
+                    mt = __shfl_sync(0xffffffffu, cand_mt, src);
+                    cnt = __shfl_sync(0xffffffffu, cand_cnt, src);
+                }
+            }
+            if (lane == 0) {
+                const uint32_t d = sidx % SCHED, ph = (sidx / SCHED) & 1u;
+                ok = wait_bounded(smem_u32(&ctrl->sched_empty[d]), ph ^ 1u, abort_flag, err, ERR_WAIT_SCHED_EMPTY);
+                if (ok) {
+                    ctrl->tile_slot[d] = mt;
+                    ctrl->tile_cnt[d] = cnt;
+                    mbar_arrive(smem_u32(&ctrl->sched_full[d]));
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            sidx++;
+            if (mt < 0 || !ok) break;
             if (cnt == 0) continue;
+
             const int mi = mt / mj_n, mj = mt % mj_n;
             const uint32_t *list = steps + (int64_t)mt * cap;
             const uint8_t *a_base = half_a + (int64_t)mi * k_tiles * A_SLAB_BYTES;
             const uint8_t *b_base = half_b + (int64_t)mj * B_SLAB_BYTES;
+            uint32_t next = (lane < cnt) ? __ldg(list + lane) : 0u;
             for (int i0 = 0; i0 < cnt && ok; i0 += 32) {
-                const uint32_t mine = (i0 + lane < cnt) ? __ldg(list + i0 + lane) : 0u;
+                const uint32_t mine = next;
+                // fetch the following 32 steps while these are being issued
+                next = (i0 + 32 + lane < cnt) ? __ldg(list + i0 + 32 + lane) : 0u;
                 const int nb = min(32, cnt - i0);
                 for (int j = 0; j < nb; j++) {
                     const uint32_t w = __shfl_sync(0xffffffffu, mine, j);
@@ -278,9 +374,14 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         if (lane == 0) {
             uint32_t slot = 0, acc_iter = 0;
             bool ok = true;
-            for (int ti = blockIdx.x; ti < n_mt && ok; ti += gridDim.x) {
-                const int mt = order ? order[ti] : ti;
-                const int cnt = step_counts[mt];
+            for (uint32_t sidx = 0; ok; sidx++) {
+                const uint32_t d = sidx % SCHED, sph = (sidx / SCHED) & 1u;
+                ok = wait_bounded(smem_u32(&ctrl->sched_full[d]), sph, abort_flag, err, ERR_WAIT_SCHED_FULL);
+                if (!ok) break;
+                const int mt = ctrl->tile_slot[d];
+                const int cnt = ctrl->tile_cnt[d];
+                mbar_arrive(smem_u32(&ctrl->sched_empty[d]));
+                if (mt < 0) break;
                 if (cnt == 0) continue;
                 const uint32_t buf = acc_iter & 1u;
                 ok = wait_bounded(smem_u32(&ctrl->tmem_empty[buf]), ((acc_iter >> 1) & 1u) ^ 1u, abort_flag, err,
@@ -305,10 +406,10 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                         const int len = __ffs(~shifted) - 1;
                         const uint32_t n = (uint32_t)len * TILE;
                         const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-                        const uint32_t d = tmem_base + buf * ACC_COLS + (uint32_t)c0 * TILE;
+                        const uint32_t dcol = tmem_base + buf * ACC_COLS + (uint32_t)c0 * TILE;
 #pragma unroll
                         for (uint32_t ks = 0; ks < 2; ks++) {
-                            umma_f16(d, smem_desc(a_addr + ks * 256u),
+                            umma_f16(dcol, smem_desc(a_addr + ks * 256u),
                                      smem_desc(b_addr + (uint32_t)c0 * TILE_BYTES + ks * 256u), idesc, m0, m1, m2, m3);
                         }
                         rest &= ~(((1u << len) - 1u) << c0);
@@ -328,26 +429,66 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             }
         }
         __syncwarp();
+    } else if (warp >= 6) {
+        // ------------------------------------------------------------------ fillers (4 warps)
+        // While the pipeline above works through the macro tiles that have steps, these warps already write the
+        // macro tiles that are all zeros, so the memory system is busy from the start.  Every two warps form a
+        // group of 64 threads that claims four macro tiles at a time from the same counter the scheduler uses for
+        // its second phase; the next claim is issued before the current tiles are written.
+        const unsigned int busy_n = sc->busy_count;
+        if (busy_n * 4u <= n_mt) {
+            const int pair_lane = threadIdx.x & 63;          // index inside the group of two warps
+            const uint32_t bar_id = 1u + (uint32_t)((warp - 6) >> 1);
+            volatile int32_t *claim = &ctrl->filler_claim[(warp - 6) >> 1][0];
+            auto claim_chunk = [&]() {
+                // first four threads of the group: one candidate each
+                if (pair_lane == 0) ctrl->filler_base[(warp - 6) >> 1] = atomicAdd(&sc->queue_all, 4u);
+                asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+                const unsigned int p0 = ctrl->filler_base[(warp - 6) >> 1];
+                if (pair_lane < 4) {
+                    int m = -1;
+                    if (p0 + pair_lane < n_mt) {
+                        m = order ? order[p0 + pair_lane] : (int)(p0 + pair_lane);
+                        if (step_counts[m] > 0) m = -1;      // handled by the pipeline
+                    }
+                    claim[pair_lane] = m;
+                }
+                asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+                return p0 < n_mt;
+            };
+            bool more = claim_chunk();
+            while (more) {
+                int m[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) m[i] = claim[i];
+                asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");   // everyone has read the claim
+                more = claim_chunk();
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    if (m[i] >= 0)
+                        zero_fill_macro_tile(c, ldc, m[i] / mj_n, m[i] % mj_n, rows_total, n_tiles * TILE, pair_lane,
+                                             64);
+            }
+        }
     } else {
         // ------------------------------------------------------------------ epilogue (4 warps)
         const uint32_t q = (uint32_t)(warp & 3);
         const int e = threadIdx.x - 64;
         uint32_t acc_iter = 0;
         bool ok = true;
-        for (int ti = blockIdx.x; ti < n_mt && ok; ti += gridDim.x) {
-            const int mt = order ? order[ti] : ti;
-            const int cnt = step_counts[mt];
+        for (uint32_t sidx = 0; ok; sidx++) {
+            const uint32_t d = sidx % SCHED, sph = (sidx / SCHED) & 1u;
+            ok = wait_bounded(smem_u32(&ctrl->sched_full[d]), sph, abort_flag, err, ERR_WAIT_SCHED_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const int mt = ctrl->tile_slot[d];
+            const int cnt = ctrl->tile_cnt[d];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[d]));
+            if (mt < 0) break;
             const int mi = mt / mj_n, mj = mt % mj_n;
             if (cnt == 0) {
-                const int col = mj * (MT_C * TILE) + (e & 63) * 4;
-                if (col < n_tiles * TILE) {
-                    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                    for (int rr = 0; rr < 64; rr++) {
-                        const int row = mi * (MT_R * TILE) + rr * 2 + (e >> 6);
-                        if (row < rows_total) __stcs(reinterpret_cast<float4 *>(c + (int64_t)row * ldc + col), z);
-                    }
-                }
+                zero_fill_macro_tile(c, ldc, mi, mj, rows_total, n_tiles * TILE, e, 128);
                 continue;
             }
             const uint32_t buf = acc_iter & 1u;
@@ -397,17 +538,19 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
 }  // namespace spamm
 
 extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
-                                        const int32_t *d_step_counts, int row_tiles, int k_tiles, int n_tiles,
-                                        float *d_c, int64_t ldc, int32_t *d_error, void *stream)
+                                        const int32_t *d_step_counts, const int32_t *d_order,
+                                        const int32_t *d_busy_list, spamm_list_scalars *d_scalars, int row_tiles,
+                                        int k_tiles, int n_tiles, float *d_c, int64_t ldc, void *stream)
 {
     using namespace spamm;
-    if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_c || !d_error || row_tiles < 0 || k_tiles < 0 ||
-        n_tiles < 0 || ldc < (int64_t)n_tiles * TILE || (ldc & 3) || (reinterpret_cast<uintptr_t>(d_c) & 15) ||
-        (reinterpret_cast<uintptr_t>(d_half_a) & 15) || (reinterpret_cast<uintptr_t>(d_half_b) & 15))
+    if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
+        k_tiles < 0 || n_tiles < 0 || ldc < (int64_t)n_tiles * TILE || (ldc & 3) ||
+        (reinterpret_cast<uintptr_t>(d_c) & 15) || (reinterpret_cast<uintptr_t>(d_half_a) & 15) ||
+        (reinterpret_cast<uintptr_t>(d_half_b) & 15) || (reinterpret_cast<uintptr_t>(d_scalars) & 7))
         return SPAMM_ERR_INVALID;
     const int64_t n_mt = (int64_t)ceil_div(row_tiles, MT_R) * ceil_div(n_tiles, MT_C);
     if (n_mt == 0) return SPAMM_OK;
-    if (n_mt > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+    if (n_mt > 0x3fffffffLL) return SPAMM_ERR_UNSUPPORTED;
 
     static thread_local int configured_device = -1;
     static thread_local int sm_count = 0;
@@ -422,10 +565,12 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
         sm_count = prop.multiProcessorCount;
         configured_device = dev;
     }
+    // the two work counters start from zero at every launch
+    SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 2 * sizeof(unsigned int), (cudaStream_t)stream));
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
     gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, (cudaStream_t)stream>>>(
         static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
-        nullptr, row_tiles, k_tiles, n_tiles, d_c, ldc, d_error);
+        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -4,7 +4,8 @@
 // The reference converts whole matrices to half on the host when it generates them (tool.cu:418); with float
 // host matrices as the interface the conversion has to happen on the GPU, and only the tiles that survive the
 // threshold are ever read by the multiply, so only those are converted (a tile of A is needed iff some list of
-// its tile row names its k; the flags come from the list builder).
+// its tile row names its k; the list builder appends every such tile once to a work list, which this kernel walks
+// with one warp per tile).
 //
 // Packed tile (2 KiB): element (o, kk) at byte (o/8)*512 + (kk/8)*128 + (o%8)*16 + (kk%8)*2, i.e. 8x8 "core
 // matrices" of 128 contiguous bytes, the K-major no-swizzle operand layout of tcgen05.mma.  For A, o is the row
@@ -29,10 +30,9 @@ __device__ __forceinline__ uint4 pack8(const float *f)
 }
 
 __global__ void __launch_bounds__(256)
-pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int row_tiles, int k_tiles, int n_tiles,
-                 const uint8_t *__restrict__ need_a, const uint8_t *__restrict__ need_b,
-                 uint8_t *__restrict__ half_a, uint8_t *__restrict__ half_b,
-                 unsigned long long *__restrict__ packed_tiles)
+pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k_tiles, int n_tiles,
+                 const uint32_t *__restrict__ tile_list, spamm_list_scalars *__restrict__ sc,
+                 uint8_t *__restrict__ half_a, uint8_t *__restrict__ half_b)
 {
     __shared__ float tr[8][TILE][TILE + 1];
     __shared__ unsigned int blk_cnt[2];
@@ -40,22 +40,20 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int r
     if (threadIdx.x < 2) blk_cnt[threadIdx.x] = 0;
     __syncthreads();
 
-    const int mi_n = (row_tiles + MT_R - 1) / MT_R;
     const int mj_n = (n_tiles + MT_C - 1) / MT_C;
-    const int64_t a_tiles = (int64_t)mi_n * k_tiles * MT_R;   // slab-major: [mi][k][quarter]
-    const int64_t b_tiles = (int64_t)k_tiles * mj_n * MT_C;   // [k][mj][column]
-    const int64_t total = a_tiles + b_tiles;
     const int64_t K = (int64_t)k_tiles * TILE, N = (int64_t)n_tiles * TILE;
+    const unsigned int n_list = sc->tile_count;
     unsigned int cnt_a = 0, cnt_b = 0;
 
-    for (int64_t t = (int64_t)blockIdx.x * 8 + warp; t < total; t += (int64_t)gridDim.x * 8) {
-        if (t < a_tiles) {
-            const int64_t slab = t >> 2;
-            const int q = (int)(t & 3);
-            if (!((need_a[slab] >> q) & 1u)) continue;
+    // one warp per listed tile
+    for (unsigned int t = blockIdx.x * 8 + warp; t < n_list; t += gridDim.x * 8) {
+        const uint32_t id = tile_list[t];
+        const int sub = (int)(id & 7u);
+        const int64_t slab = (int64_t)((id & 0x7fffffffu) >> 3);
+        if (!(id & 0x80000000u)) {
             const int mi = (int)(slab / k_tiles), k = (int)(slab % k_tiles);
-            const float *src = a + ((int64_t)(mi * MT_R + q) * TILE) * K + (int64_t)k * TILE;
-            uint8_t *dst = half_a + slab * A_SLAB_BYTES + q * TILE_BYTES;
+            const float *src = a + ((int64_t)(mi * MT_R + sub) * TILE) * K + (int64_t)k * TILE;
+            uint8_t *dst = half_a + slab * A_SLAB_BYTES + sub * TILE_BYTES;
 #pragma unroll
             for (int it = 0; it < 4; it++) {
                 const int row = it * 8 + (lane >> 2), kg = lane & 3;
@@ -66,13 +64,9 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int r
             }
             cnt_a++;
         } else {
-            const int64_t tb = t - a_tiles;
-            const int64_t slab = tb >> 3;
-            const int c = (int)(tb & 7);
-            if (!((need_b[slab] >> c) & 1u)) continue;
             const int k = (int)(slab / mj_n), mj = (int)(slab % mj_n);
-            const float *src = b + ((int64_t)k * TILE) * N + (int64_t)(mj * MT_C + c) * TILE;
-            uint8_t *dst = half_b + slab * B_SLAB_BYTES + c * TILE_BYTES;
+            const float *src = b + ((int64_t)k * TILE) * N + (int64_t)(mj * MT_C + sub) * TILE;
+            uint8_t *dst = half_b + slab * B_SLAB_BYTES + sub * TILE_BYTES;
             __syncwarp();
 #pragma unroll 8
             for (int kk = 0; kk < TILE; kk++) tr[warp][kk][lane] = src[(int64_t)kk * N + lane];
@@ -92,32 +86,32 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int r
         if (cnt_b) atomicAdd(&blk_cnt[1], cnt_b);
     }
     __syncthreads();
-    if (threadIdx.x < 2 && blk_cnt[threadIdx.x])
-        atomicAdd(packed_tiles + threadIdx.x, (unsigned long long)blk_cnt[threadIdx.x]);
+    if (threadIdx.x == 0 && blk_cnt[0]) atomicAdd(&sc->packed_a, blk_cnt[0]);
+    if (threadIdx.x == 1 && blk_cnt[1]) atomicAdd(&sc->packed_b, blk_cnt[1]);
 }
 
 }  // namespace spamm
 
 extern "C" int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
-                                   const uint8_t *d_need_a, const uint8_t *d_need_b, void *d_half_a,
-                                   void *d_half_b, unsigned long long *d_packed_tiles, void *stream)
+                                   const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a,
+                                   void *d_half_b, void *stream)
 {
     using namespace spamm;
-    if (!d_a || !d_b || !d_need_a || !d_need_b || !d_half_a || !d_half_b || !d_packed_tiles || row_tiles < 0 ||
-        k_tiles < 0 || n_tiles < 0)
+    if (!d_a || !d_b || !d_tile_list || !d_scalars || !d_half_a || !d_half_b || row_tiles < 0 || k_tiles < 0 ||
+        n_tiles < 0)
         return SPAMM_ERR_INVALID;
     if ((reinterpret_cast<uintptr_t>(d_a) & 15) || (reinterpret_cast<uintptr_t>(d_b) & 15) ||
         (reinterpret_cast<uintptr_t>(d_half_a) & 15) || (reinterpret_cast<uintptr_t>(d_half_b) & 15))
         return SPAMM_ERR_INVALID;
-    const int64_t total = (int64_t)ceil_div(row_tiles, MT_R) * k_tiles * MT_R +
-                          (int64_t)k_tiles * ceil_div(n_tiles, MT_C) * MT_C;
+    const int64_t total = ((int64_t)ceil_div(row_tiles, MT_R) * MT_R + (int64_t)ceil_div(n_tiles, MT_C) * MT_C) * k_tiles;
     if (total == 0) return SPAMM_OK;
+    // the number of listed tiles is known only on the device: a fixed grid strides over the list
     int64_t blocks = (total + 7) / 8;
-    const int64_t max_blocks = 148 * 16;
+    const int64_t max_blocks = 148 * 8;
     if (blocks > max_blocks) blocks = max_blocks;
     pack_half_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-        d_a, d_b, row_tiles, k_tiles, n_tiles, d_need_a, d_need_b, static_cast<uint8_t *>(d_half_a),
-        static_cast<uint8_t *>(d_half_b), d_packed_tiles);
+        d_a, d_b, k_tiles, n_tiles, d_tile_list, d_scalars, static_cast<uint8_t *>(d_half_a),
+        static_cast<uint8_t *>(d_half_b));
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

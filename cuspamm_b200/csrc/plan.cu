@@ -23,13 +23,8 @@ int record_cuda_error(cudaError_t e, const char *what)
 // Stores a detail message for spamm_last_cuda_error when the failing call is not a CUDA runtime call.
 void record_error_text(const char *text) { g_last_cuda_error = text; }
 
-// Scalars the kernels write; lives at the head of the buffer that is cleared before every list build.
-struct DeviceScalars {
-    unsigned long long survivors;
-    unsigned long long packed[2];
-    int32_t overflow;
-    int32_t error;
-};
+// The kernels' counters live at the head of the buffer that is cleared before every list build.
+using DeviceScalars = spamm_list_scalars;
 
 }  // namespace spamm
 
@@ -46,6 +41,10 @@ struct spamm_plan {
     int32_t *d_counts = nullptr, *d_step_counts = nullptr;
     uint32_t *d_steps = nullptr;
     uint8_t *d_half_a = nullptr, *d_half_b = nullptr;
+    int32_t *d_order = nullptr;         // macro-tile visiting order of the multiply kernel
+    int32_t *d_busy = nullptr;          // macro tiles that have steps
+    uint32_t *d_tile_list = nullptr;    // tiles to convert to half
+    void *d_list_scratch = nullptr;     // chunk maxima of the list builder
     uint8_t *d_cleared = nullptr;       // [DeviceScalars | need_a | need_b], cleared per list build
     size_t cleared_bytes = 0, need_a_off = 0, need_b_off = 0;
     DeviceScalars *h_scalars = nullptr; // pinned
@@ -168,6 +167,19 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     if ((st = dev_alloc(&p->d_steps, p->bytes_steps()))) return fail(st);
     if ((st = dev_alloc(&p->d_half_a, p->bytes_half_a()))) return fail(st);
     if ((st = dev_alloc(&p->d_half_b, p->bytes_half_b()))) return fail(st);
+    if ((st = dev_alloc(&p->d_order, p->bytes_step_counts()))) return fail(st);
+    if ((st = dev_alloc(&p->d_busy, p->bytes_step_counts()))) return fail(st);
+    if ((st = dev_alloc(&p->d_tile_list,
+                        sizeof(uint32_t) * ((size_t)p->mi_n * MT_R + (size_t)p->mj_n * MT_C) * p->k_tiles)))
+        return fail(st);
+    if ((st = dev_alloc(&p->d_list_scratch, spamm_build_lists_scratch_bytes(p->row_tiles, p->k_tiles, p->n_tiles))))
+        return fail(st);
+    if (p->n_mt()) {
+        std::vector<int32_t> order(p->n_mt());
+        spamm_macro_tile_order(p->row_tiles, p->n_tiles, order.data());
+        if (cudaMemcpy(p->d_order, order.data(), p->bytes_step_counts(), cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail(record_cuda_error(cudaGetLastError(), "cudaMemcpy(order)"));
+    }
     p->need_a_off = round_up(sizeof(DeviceScalars), 16);
     p->need_b_off = p->need_a_off + round_up((size_t)p->mi_n * p->k_tiles, 16);
     p->cleared_bytes = p->need_b_off + round_up((size_t)p->k_tiles * p->mj_n, 16);
@@ -195,7 +207,8 @@ int spamm_plan_destroy(spamm_plan *p)
     cudaFree(p->d_a); cudaFree(p->d_b); cudaFree(p->d_c);
     cudaFree(p->d_norm_a); cudaFree(p->d_norm_b);
     cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
-    cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared);
+    cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared); cudaFree(p->d_order);
+    cudaFree(p->d_busy); cudaFree(p->d_tile_list); cudaFree(p->d_list_scratch);
     cudaFree(p->d_cv_scratch); cudaFree(p->d_cv_count);
     if (p->h_scalars) cudaFreeHost(p->h_scalars);
     if (p->h_cv) cudaFreeHost(p->h_cv);
@@ -252,11 +265,11 @@ int spamm_build_lists(spamm_plan *p, float tau)
     DeviceGuard guard(p->device);
     SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
     if (p->row_tiles) {
-        int st = spamm_build_lists_dev(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau, p->d_steps,
-                                       p->d_step_counts, p->d_counts, &p->scalars()->survivors, p->need_a(),
-                                       p->need_b(), &p->scalars()->overflow, p->stream);
+        int st = spamm_build_lists_dev(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
+                                       p->d_list_scratch, p->d_steps, p->d_step_counts, p->d_counts, p->need_a(),
+                                       p->need_b(), p->d_tile_list, p->d_busy, p->scalars(), p->stream);
         if (st) return st;
-        p->launches++;
+        p->launches += 2;
     }
     p->have_lists = true;
     p->have_pack = false;
@@ -269,8 +282,8 @@ int spamm_pack(spamm_plan *p)
     if (!p->have_lists) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     if (p->row_tiles) {
-        int st = spamm_pack_half_dev(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->need_a(), p->need_b(),
-                                     p->d_half_a, p->d_half_b, p->scalars()->packed, p->stream);
+        int st = spamm_pack_half_dev(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->d_tile_list,
+                                     p->scalars(), p->d_half_a, p->d_half_b, p->stream);
         if (st) return st;
         p->launches++;
     }
@@ -284,8 +297,8 @@ int spamm_gated_multiply(spamm_plan *p)
     if (!p->have_pack) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     if (p->row_tiles) {
-        int st = spamm_gated_multiply_dev(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->row_tiles,
-                                          p->k_tiles, p->n_tiles, p->d_c, p->N, &p->scalars()->error, p->stream);
+        int st = spamm_gated_multiply_dev(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
+                                          p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, p->stream);
         if (st) return st;
         p->launches++;
     }
@@ -324,8 +337,8 @@ static void fill_stats(spamm_plan *p, spamm_stats *s)
 {
     s->survivors = (int64_t)p->h_scalars->survivors;
     s->tile_products = (int64_t)p->row_tiles * p->k_tiles * p->n_tiles;
-    s->packed_tiles_a = (int64_t)p->h_scalars->packed[0];
-    s->packed_tiles_b = (int64_t)p->h_scalars->packed[1];
+    s->packed_tiles_a = (int64_t)p->h_scalars->packed_a;
+    s->packed_tiles_b = (int64_t)p->h_scalars->packed_b;
     s->executed_flops = 65536.0 * (double)s->survivors;
 }
 
@@ -497,6 +510,20 @@ int spamm_get_lists(spamm_plan *p, int64_t *offsets, int32_t *k_idx)
             }
         }
     }
+    return SPAMM_OK;
+}
+
+int spamm_macro_tile_order(int row_tiles, int n_tiles, int32_t *order)
+{
+    if (row_tiles < 0 || n_tiles < 0 || !order) return SPAMM_ERR_INVALID;
+    const int mi_n = ceil_div(row_tiles, MT_R), mj_n = ceil_div(n_tiles, MT_C);
+    // Bands of 16 macro-tile rows, walked column by column: about 148 consecutive entries (one per SM) then cover
+    // 16 rows x 9 columns, so a wave of blocks reads 16 slabs of A and 9 of B per k instead of 2 and 64.
+    const int band = 16;
+    size_t n = 0;
+    for (int i0 = 0; i0 < mi_n; i0 += band)
+        for (int j = 0; j < mj_n; j++)
+            for (int i = i0; i < i0 + band && i < mi_n; i++) order[n++] = i * mj_n + j;
     return SPAMM_OK;
 }
 

@@ -11,26 +11,93 @@
 // Output form: a "step" names one k, a set of tile rows and a set of tile columns whose every pair survives.
 // For one k the rows selected in a column form nested sets (the float product is monotone in either factor),
 // so grouping columns by equal row set loses nothing: the steps of a k are disjoint and cover the survivors.
+//
+// Pruning: a first small kernel takes, per group of 4 tile rows of A (8 tile columns of B) and chunk of 32 k, the
+// largest norm.  Rounded float multiplication is monotone in each factor, so when the product of the two largest
+// norms of a chunk is below the threshold, every product of the chunk is: the builder skips the chunk without
+// reading it, and the result is still exact.
+//
+// By-products for the next two kernels: the list of distinct tiles of A and of B that some step names (what has to
+// be converted to half) and the list of macro tiles that have at least one step (scheduled first by the multiply).
 #include "common.cuh"
 
 namespace spamm {
 
-__device__ __forceinline__ void or_flag_byte(uint8_t *base, int64_t idx, uint32_t bits)
-{
-    unsigned int *w = reinterpret_cast<unsigned int *>(base + (idx & ~int64_t(3)));
-    const unsigned int v = bits << (8 * (unsigned)(idx & 3));
-    if ((*reinterpret_cast<volatile unsigned int *>(w) & v) != v) atomicOr(w, v);
-}
-
-__global__ void __launch_bounds__(128)
-build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
-                   int n_tiles, float tau, uint32_t *__restrict__ steps, int32_t *__restrict__ step_counts,
-                   int32_t *__restrict__ counts, unsigned long long *__restrict__ survivors,
-                   uint8_t *__restrict__ need_a, uint8_t *__restrict__ need_b, int32_t *__restrict__ overflow)
+// amax[mi][kc] = max |nA| over tile rows 4mi..4mi+3 and k in chunk kc; bmax[kc][mj] = max |nB| over k in chunk kc and
+// tile columns 8mj..8mj+7.  One warp per output value.
+__global__ void __launch_bounds__(256)
+chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
+                 int n_tiles, float *__restrict__ amax, float *__restrict__ bmax)
 {
     const int lane = threadIdx.x & 31;
     const int mi_n = (row_tiles + MT_R - 1) / MT_R;
     const int mj_n = (n_tiles + MT_C - 1) / MT_C;
+    const int kc_n = (k_tiles + 31) / 32;
+    const int w = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int n_a = mi_n * kc_n, n_b = kc_n * mj_n;
+    if (w >= n_a + n_b) return;
+    float m = 0.0f;
+    bool odd = false;    // an infinite or NaN norm in the chunk
+    if (w < n_a) {
+        const int mi = w / kc_n, kc = w % kc_n;
+        const int k = kc * 32 + lane;
+        if (k < k_tiles) {
+#pragma unroll
+            for (int r = 0; r < MT_R; r++) {
+                const int row = mi * MT_R + r;
+                if (row < row_tiles) {
+                    const float v = fabsf(norm_a[(int64_t)row * k_tiles + k]);
+                    odd |= !(v <= 3.0e38f);
+                    m = fmaxf(m, v);
+                }
+            }
+        }
+    } else {
+        const int kc = (w - n_a) / mj_n, mj = (w - n_a) % mj_n;
+        // column c = lane & 7, four k per pass
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+            const int k = kc * 32 + p * 4 + (lane >> 3);
+            const int colt = mj * MT_C + (lane & 7);
+            if (k < k_tiles && colt < n_tiles) {
+                const float v = fabsf(norm_b[(int64_t)k * n_tiles + colt]);
+                odd |= !(v <= 3.0e38f);
+                m = fmaxf(m, v);
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    // a chunk with a non-finite norm is never skipped: NaN makes the builder's "product < tau" test false
+    if (__any_sync(0xffffffffu, odd)) m = __int_as_float(0x7fc00000);
+    if (lane == 0) {
+        if (w < n_a) amax[w] = m;
+        else bmax[w - n_a] = m;
+    }
+}
+
+// Sets bits of a flag byte and returns the bits that were not set before.
+__device__ __forceinline__ uint32_t or_flag_byte(uint8_t *base, int64_t idx, uint32_t bits)
+{
+    unsigned int *w = reinterpret_cast<unsigned int *>(base + (idx & ~int64_t(3)));
+    const unsigned int sh = 8 * (unsigned)(idx & 3);
+    const unsigned int v = bits << sh;
+    if ((*reinterpret_cast<volatile unsigned int *>(w) & v) == v) return 0;
+    const unsigned int old = atomicOr(w, v);
+    return ((v & ~old) >> sh) & 0xffu;
+}
+
+__global__ void __launch_bounds__(128)
+build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
+                   int n_tiles, float tau, const float *__restrict__ amax, const float *__restrict__ bmax,
+                   uint32_t *__restrict__ steps, int32_t *__restrict__ step_counts, int32_t *__restrict__ counts,
+                   uint8_t *__restrict__ need_a, uint8_t *__restrict__ need_b, uint32_t *__restrict__ tile_list,
+                   int32_t *__restrict__ busy_list, spamm_list_scalars *__restrict__ sc)
+{
+    const int lane = threadIdx.x & 31;
+    const int mi_n = (row_tiles + MT_R - 1) / MT_R;
+    const int mj_n = (n_tiles + MT_C - 1) / MT_C;
+    const int kc_n = (k_tiles + 31) / 32;
     const int mt = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (mt >= mi_n * mj_n) return;
     const int mi = mt / mj_n, mj = mt % mj_n;
@@ -40,82 +107,133 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
     int n_out = 0;       // warp-uniform
     int my_count = 0;    // lane b counts survivors of pair b = column*4 + row
 
-    for (int kb = 0; kb < k_tiles; kb += 32) {
-        const int k = kb + lane;
-        const bool k_ok = k < k_tiles;
-        uint32_t mask = 0;
-        if (k_ok) {
-            float a[MT_R];
+    // pairs (row r, column c) of this macro tile that exist, bit c*4 + r
+    uint32_t valid_bits = 0;
 #pragma unroll
-            for (int r = 0; r < MT_R; r++) {
-                const int row = mi * MT_R + r;
-                a[r] = (row < row_tiles) ? norm_a[(int64_t)row * k_tiles + k] : 0.0f;
-            }
+    for (int c = 0; c < MT_C; c++)
 #pragma unroll
-            for (int c = 0; c < MT_C; c++) {
-                const int colt = mj * MT_C + c;
-                if (colt < n_tiles) {
-                    const float b = norm_b[(int64_t)k * n_tiles + colt];
+        for (int r = 0; r < MT_R; r++)
+            if (mi * MT_R + r < row_tiles && mj * MT_C + c < n_tiles) valid_bits |= 1u << (c * 4 + r);
+    const bool b_vec = ((n_tiles & 3) == 0) && (mj * MT_C + MT_C <= n_tiles) &&
+                       ((reinterpret_cast<uintptr_t>(norm_b) & 15) == 0);
+
+    for (int g0 = 0; g0 < kc_n; g0 += 32) {
+        // which of the next 32 chunks can hold a survivor at all
+        bool alive = false;
+        if (g0 + lane < kc_n) {
+            const float pm = __fmul_rn(amax[(int64_t)mi * kc_n + g0 + lane], bmax[(int64_t)(g0 + lane) * mj_n + mj]);
+            alive = !(pm < tau);
+        }
+        uint32_t chunks = __ballot_sync(0xffffffffu, alive);
+        while (chunks) {
+            const int kb = (g0 + __ffs(chunks) - 1) * 32;
+            chunks &= chunks - 1;
+            const int k = kb + lane;
+            uint32_t mask = 0;
+            if (k < k_tiles) {
+                float a[MT_R], b[MT_C];
+#pragma unroll
+                for (int r = 0; r < MT_R; r++) {
+                    const int row = mi * MT_R + r;
+                    a[r] = (row < row_tiles) ? __ldg(norm_a + (int64_t)row * k_tiles + k) : 0.0f;
+                }
+                const float *brow = norm_b + (int64_t)k * n_tiles + mj * MT_C;
+                if (b_vec) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(brow));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4 *>(brow) + 1);
+                    b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w;
+                    b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < MT_C; c++) b[c] = (mj * MT_C + c < n_tiles) ? __ldg(brow + c) : 0.0f;
+                }
+#pragma unroll
+                for (int c = 0; c < MT_C; c++) {
 #pragma unroll
                     for (int r = 0; r < MT_R; r++) {
-                        if (mi * MT_R + r < row_tiles) {
-                            const float prod = __fmul_rn(a[r], b);
-                            if (prod >= tau) mask |= 1u << (c * 4 + r);
-                        }
+                        const float prod = __fmul_rn(a[r], b[c]);
+                        if (prod >= tau) mask |= 1u << (c * 4 + r);
                     }
+                }
+                mask &= valid_bits;
+            }
+            if (!__any_sync(0xffffffffu, mask != 0)) continue;
+            // per-tile list lengths
+#pragma unroll
+            for (int bit = 0; bit < 32; bit++) {
+                const uint32_t v = __ballot_sync(0xffffffffu, (mask >> bit) & 1u);
+                if (lane == bit) my_count += __popc(v);
+            }
+            // steps of this lane's k: columns grouped by equal row set
+            uint32_t st[MT_C];
+            int n = 0;
+            uint32_t done = 0, rows_any = 0, cols_any = 0;
+#pragma unroll
+            for (int c = 0; c < MT_C; c++) {
+                const uint32_t nib = (mask >> (4 * c)) & 0xfu;
+                uint32_t val = 0;
+                if (nib != 0 && !((done >> c) & 1u)) {
+                    uint32_t cols = 0;
+#pragma unroll
+                    for (int c2 = 0; c2 < MT_C; c2++)
+                        if (((mask >> (4 * c2)) & 0xfu) == nib) cols |= 1u << c2;
+                    done |= cols;
+                    val = step_pack((uint32_t)k, nib, cols);
+                    rows_any |= nib;
+                    cols_any |= cols;
+                }
+                st[c] = val;
+                n += (val != 0);
+            }
+            // tiles named for the first time go to the conversion list
+            uint32_t new_a = 0, new_b = 0;
+            if (rows_any) {
+                new_a = or_flag_byte(need_a, (int64_t)mi * k_tiles + k, rows_any);
+                new_b = or_flag_byte(need_b, (int64_t)k * mj_n + mj, cols_any);
+            }
+            const int n_new = __popc(new_a) + __popc(new_b);
+            // two warp prefix sums at once: steps (low 16 bits) and new tiles (high 16 bits); both are <= 12 per lane
+            uint32_t incl = (uint32_t)n | ((uint32_t)n_new << 16);
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += t;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+            const int total_steps = (int)(total & 0xffffu), total_new = (int)(total >> 16);
+            int pos = n_out + (int)(incl & 0xffffu) - n;
+            if ((int64_t)n_out + total_steps <= cap) {
+#pragma unroll
+                for (int c = 0; c < MT_C; c++) {
+                    if (st[c] != 0) out[pos++] = st[c];
+                }
+                n_out += total_steps;
+            } else if (lane == 0) {
+                atomicExch(&sc->overflow, 1);
+            }
+            if (total_new) {
+                unsigned int base = 0;
+                if (lane == 0) base = atomicAdd(&sc->tile_count, (unsigned int)total_new);
+                base = __shfl_sync(0xffffffffu, base, 0);
+                unsigned int at = base + (incl >> 16) - (unsigned int)n_new;
+                const uint32_t a_slab = (uint32_t)(mi * k_tiles + k), b_slab = (uint32_t)(k * mj_n + mj);
+                while (new_a) {
+                    const int q = __ffs(new_a) - 1;
+                    new_a &= new_a - 1;
+                    tile_list[at++] = (a_slab << 3) | (uint32_t)q;
+                }
+                while (new_b) {
+                    const int c = __ffs(new_b) - 1;
+                    new_b &= new_b - 1;
+                    tile_list[at++] = 0x80000000u | (b_slab << 3) | (uint32_t)c;
                 }
             }
         }
-        // per-tile list lengths
-#pragma unroll
-        for (int bit = 0; bit < 32; bit++) {
-            const uint32_t v = __ballot_sync(0xffffffffu, (mask >> bit) & 1u);
-            if (lane == bit) my_count += __popc(v);
-        }
-        // steps of this lane's k: columns grouped by equal row set
-        uint32_t st[MT_C];
-        int n = 0;
-        uint32_t done = 0, rows_any = 0, cols_any = 0;
-#pragma unroll
-        for (int c = 0; c < MT_C; c++) {
-            const uint32_t nib = (mask >> (4 * c)) & 0xfu;
-            uint32_t val = 0;
-            if (nib != 0 && !((done >> c) & 1u)) {
-                uint32_t cols = 0;
-#pragma unroll
-                for (int c2 = 0; c2 < MT_C; c2++)
-                    if (((mask >> (4 * c2)) & 0xfu) == nib) cols |= 1u << c2;
-                done |= cols;
-                val = step_pack((uint32_t)k, nib, cols);
-                rows_any |= nib;
-                cols_any |= cols;
-            }
-            st[c] = val;
-            n += (val != 0);
-        }
-        int incl = n;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += t;
-        }
-        const int total = __shfl_sync(0xffffffffu, incl, 31);
-        int pos = n_out + incl - n;
-        if ((int64_t)n_out + total <= cap) {
-#pragma unroll
-            for (int c = 0; c < MT_C; c++) {
-                if (st[c] != 0) out[pos++] = st[c];
-            }
-            n_out += total;
-        } else if (lane == 0) {
-            atomicExch(overflow, 1);
-        }
-        if (rows_any) {
-            or_flag_byte(need_a, (int64_t)mi * k_tiles + k, rows_any);
-            or_flag_byte(need_b, (int64_t)k * mj_n + mj, cols_any);
-        }
     }
-    if (lane == 0) step_counts[mt] = n_out;
+    if (lane == 0) {
+        step_counts[mt] = n_out;
+        if (n_out > 0) busy_list[atomicAdd(&sc->busy_count, 1u)] = mt;
+    }
     {
         const int r = lane & 3, c = lane >> 2;
         const int row = mi * MT_R + r, colt = mj * MT_C + c;
@@ -124,29 +242,47 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
     unsigned int s = (unsigned int)my_count;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-    if (lane == 0 && s) atomicAdd(survivors, (unsigned long long)s);
+    if (lane == 0 && s) atomicAdd(&sc->survivors, (unsigned long long)s);
 }
 
 }  // namespace spamm
 
-extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles,
-                                     int n_tiles, float tau, uint32_t *d_steps, int32_t *d_step_counts,
-                                     int32_t *d_counts, unsigned long long *d_survivors, uint8_t *d_need_a,
-                                     uint8_t *d_need_b, int32_t *d_overflow, void *stream)
+extern "C" size_t spamm_build_lists_scratch_bytes(int row_tiles, int k_tiles, int n_tiles)
 {
     using namespace spamm;
-    if (!d_norm_a || !d_norm_b || !d_steps || !d_step_counts || !d_counts || !d_survivors || !d_need_a ||
-        !d_need_b || !d_overflow || row_tiles < 0 || k_tiles < 0 || n_tiles < 0 || k_tiles > 65535)
+    if (row_tiles < 0 || k_tiles < 0 || n_tiles < 0) return 0;
+    const size_t kc_n = (size_t)(k_tiles + 31) / 32;
+    return sizeof(float) * kc_n * ((size_t)ceil_div(row_tiles, MT_R) + ceil_div(n_tiles, MT_C)) + 16;
+}
+
+extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles,
+                                     int n_tiles, float tau, void *d_scratch, uint32_t *d_steps,
+                                     int32_t *d_step_counts, int32_t *d_counts, uint8_t *d_need_a, uint8_t *d_need_b,
+                                     uint32_t *d_tile_list, int32_t *d_busy_list, spamm_list_scalars *d_scalars,
+                                     void *stream)
+{
+    using namespace spamm;
+    if (!d_norm_a || !d_norm_b || !d_scratch || !d_steps || !d_step_counts || !d_counts || !d_need_a || !d_need_b ||
+        !d_tile_list || !d_busy_list || !d_scalars || row_tiles < 0 || k_tiles < 0 || n_tiles < 0 || k_tiles > 65535)
         return SPAMM_ERR_INVALID;
-    if ((reinterpret_cast<uintptr_t>(d_need_a) & 3) || (reinterpret_cast<uintptr_t>(d_need_b) & 3))
+    if ((reinterpret_cast<uintptr_t>(d_need_a) & 3) || (reinterpret_cast<uintptr_t>(d_need_b) & 3) ||
+        (reinterpret_cast<uintptr_t>(d_scratch) & 3) || (reinterpret_cast<uintptr_t>(d_scalars) & 7))
         return SPAMM_ERR_INVALID;
-    const int64_t mts = (int64_t)ceil_div(row_tiles, MT_R) * ceil_div(n_tiles, MT_C);
+    const int mi_n = ceil_div(row_tiles, MT_R), mj_n = ceil_div(n_tiles, MT_C), kc_n = ceil_div(k_tiles, 32);
+    const int64_t mts = (int64_t)mi_n * mj_n;
     if (mts == 0) return SPAMM_OK;
     const int64_t blocks = (mts + 3) / 4;
-    if (blocks > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+    if (blocks > 0x7fffffffLL || (int64_t)mi_n * k_tiles >= (1LL << 28) || (int64_t)k_tiles * mj_n >= (1LL << 28))
+        return SPAMM_ERR_UNSUPPORTED;
+    float *amax = static_cast<float *>(d_scratch);
+    float *bmax = amax + (size_t)mi_n * kc_n;
+    const int64_t warps = (int64_t)kc_n * (mi_n + mj_n);
+    if (warps > 0)
+        chunk_max_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(d_norm_a, d_norm_b, row_tiles,
+                                                                                       k_tiles, n_tiles, amax, bmax);
     build_lists_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(
-        d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, d_steps, d_step_counts, d_counts, d_survivors,
-        d_need_a, d_need_b, d_overflow);
+        d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, amax, bmax, d_steps, d_step_counts, d_counts, d_need_a,
+        d_need_b, d_tile_list, d_busy_list, d_scalars);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

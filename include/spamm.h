@@ -62,6 +62,22 @@ typedef struct spamm_stats {
     double executed_flops;      /* 65536 * S */
 } spamm_stats;
 
+/*
+ * Counters the list builder, the packing kernel and the multiply kernel keep in device memory (one per problem).
+ * The caller of the kernel-level entry points clears the whole structure before spamm_build_lists_dev.
+ */
+typedef struct spamm_list_scalars {
+    unsigned long long survivors;   /* S, written by the list builder */
+    unsigned int tile_count;        /* entries of the list of tiles to convert to half */
+    unsigned int busy_count;        /* entries of the list of macro tiles that have steps */
+    unsigned int packed_a;          /* tiles of A converted by the packing kernel */
+    unsigned int packed_b;          /* tiles of B converted by the packing kernel */
+    unsigned int queue_busy;        /* work counters of the multiply kernel; every multiply call resets the two */
+    unsigned int queue_all;
+    int32_t overflow;               /* non-zero: a step list did not fit */
+    int32_t error;                  /* non-zero: a bounded wait of the multiply kernel ran out (which one) */
+} spamm_list_scalars;
+
 /* Names for spamm_device_buffer. */
 typedef enum spamm_buffer {
     SPAMM_BUF_A = 0,            /* float  [row_tile_count*32][K]   this plan's rows of A                      */
@@ -182,35 +198,51 @@ int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t ld, float *
  * SPAMM_MT_ROWS x SPAMM_MT_COLS C tiles it writes a list of steps, ascending in k; a step is
  *     bits 0-15  k,   bits 16-19  which of the 4 tile rows take part,   bits 20-27  which of the 8 tile columns,
  * and every (row, column) pair of a step is a surviving product, every surviving product is in exactly one step.
- * d_steps holds step_capacity (= 8*(K/32)) words per macro tile, macro tiles in row-major order.
- * d_counts[row_tiles][N/32] receives the per-tile list lengths, *d_survivors their sum.
- * d_need_a / d_need_b (one byte per A slab of 4 tiles / B slab of 8 tiles; must be zero on entry) receive the
- * tiles that appear in some list.  d_overflow is set non-zero if a list did not fit.
+ * The norm maps must be non-negative (they are norms).
+ *   d_scratch      work space of spamm_build_lists_scratch_bytes(...) bytes (chunk maxima used for pruning)
+ *   d_steps        8*(K/32) words per macro tile, macro tiles in row-major order
+ *   d_step_counts  [macro tiles] number of steps written
+ *   d_counts       [row_tiles][N/32] per-tile list lengths
+ *   d_need_a/_b    one byte per A slab of 4 tiles / B slab of 8 tiles, a bit per tile that some step names;
+ *                  must be zero on entry
+ *   d_tile_list    every named tile once: bit 31 = tile of B, bits 3-30 = slab index, bits 0-2 = tile in the slab;
+ *                  room for (4*ceil(row_tiles/4) + 8*ceil(n_tiles/8)) * (K/32) entries
+ *   d_busy_list    the macro tiles with at least one step, in no particular order; room for all macro tiles
+ *   d_scalars      zero on entry; receives S, the two list lengths and the overflow flag
  */
+size_t spamm_build_lists_scratch_bytes(int row_tiles, int k_tiles, int n_tiles);
 int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,
-                          float tau, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
-                          unsigned long long *d_survivors, uint8_t *d_need_a, uint8_t *d_need_b,
-                          int32_t *d_overflow, void *stream);
+                          float tau, void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
+                          uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list, int32_t *d_busy_list,
+                          spamm_list_scalars *d_scalars, void *stream);
 
 /*
- * float -> half (round to nearest even, as __float2half at tool.cu:418) of the flagged 32x32 tiles into the
+ * float -> half (round to nearest even, as __float2half at tool.cu:418) of the listed 32x32 tiles into the
  * packed layout the multiply kernel loads: every tile is 2 KiB,
  *     byte offset of element (o, kk) = (o/8)*512 + (kk/8)*128 + (o%8)*16 + (kk%8)*2,
  * o = row of an A tile / column of a B tile, kk = the index that is summed over.  A tiles are grouped
  * 4 (rows) to a slab, slabs ordered [row group][k]; B tiles 8 (columns) to a slab, slabs ordered [k][column group].
+ * d_tile_list and d_scalars->tile_count come from spamm_build_lists_dev.
  */
 int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
-                        const uint8_t *d_need_a, const uint8_t *d_need_b, void *d_half_a, void *d_half_b,
-                        unsigned long long *d_packed_tiles, void *stream);
+                        const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
+                        void *stream);
 
 /*
  * Gated multiply (get_C_FP16_B32, cuSpAMM.cu:336-391): walks the step lists, multiplies on the tensor cores
  * (half inputs, float accumulation) and writes every C tile of the block, zeros where a list is empty.
- * d_error (one int32, zero on entry) is set non-zero if a bounded device wait ran out.
+ * d_order (may be NULL = row-major) is a permutation of the macro-tile indices: the order in which the resident
+ * blocks take macro tiles from the work queue; spamm_macro_tile_order fills one that keeps concurrently processed
+ * macro tiles close together in both directions, so that they share operand tiles in L2.  When few macro tiles
+ * have steps, those (d_busy_list) are taken first.
+ * d_scalars->error is set non-zero if a bounded device wait ran out.
  */
 int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
-                             const int32_t *d_step_counts, int row_tiles, int k_tiles, int n_tiles,
-                             float *d_c, int64_t ldc, int32_t *d_error, void *stream);
+                             const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
+                             spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
+                             int64_t ldc, void *stream);
+/* Host helper: writes the macro-tile order described above into order[ceil(row_tiles/4)*ceil(n_tiles/8)]. */
+int spamm_macro_tile_order(int row_tiles, int n_tiles, int32_t *order);
 
 /*
  * countValid (tool.cu:493-529) on caller memory: *d_count = #{(i,k,j): nA(i,k)*nB(k,j) >= tau}, *d_sum (may be

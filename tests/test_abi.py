@@ -49,7 +49,7 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.spamm_norms(None) == 1
     assert lib.spamm_norm_map_dev(None, 32, 32, 32, None, None) == 1
     assert lib.spamm_norm_map_dev(C.c_void_p(16), 33, 32, 32, C.c_void_p(16), None) == 1
-    assert lib.spamm_gated_multiply_dev(None, None, None, None, 1, 1, 1, None, 32, None, None) == 1
+    assert lib.spamm_gated_multiply_dev(None, None, None, None, None, None, None, 1, 1, 1, None, 32, None) == 1
     assert lib.spamm_count_valid_scratch_bytes(512, 512) == 512 * 2 * 16
 
 
@@ -107,3 +107,11 @@ def test_row_blocks():
         if tiles >= 4 * world:
             assert all(b % 4 == 0 for b, _ in blocks)
     assert row_blocks(512, 8) == [(64 * r, 64) for r in range(8)]     # the reference's T/G split
+
+
+def test_macro_tile_order_is_a_permutation(lib):
+    for row_tiles, n_tiles in [(512, 512), (64, 512), (5, 9), (1, 1), (130, 70)]:
+        n = ((row_tiles + 3) // 4) * ((n_tiles + 7) // 8)
+        order = np.full(n, -1, dtype=np.int32)
+        assert lib.spamm_macro_tile_order(row_tiles, n_tiles, order.ctypes.data) == 0
+        assert np.array_equal(np.sort(order), np.arange(n))
