@@ -185,7 +185,7 @@ extern "C" int spamm_count_valid_static(const float *d_norm_a, const float *d_no
     if (!d_norm_a || !d_norm_b || !d_count || row_tiles < 0 || k_tiles < 0 || n_tiles < 0) return SPAMM_ERR_INVALID;
     const int64_t blocks = count_valid_blocks(row_tiles, n_tiles);
     if (blocks > CV_STATIC_MAX_BLOCKS) {
-        static thread_local char msg[160];
+        static thread_local char msg[224];
         snprintf(msg, sizeof(msg),
                  "spamm_count_valid_static: %lld partial sums needed (row_tiles * ceil(n_tiles/256)), the built-in "
                  "array holds %d; use spamm_count_valid_dev with caller scratch",

@@ -24,7 +24,10 @@
 
 namespace spamm {
 
-constexpr int STAGES = 6;
+#ifndef SPAMM_STAGES
+#define SPAMM_STAGES 6
+#endif
+constexpr int STAGES = SPAMM_STAGES;
 constexpr int STAGE_BYTES = A_SLAB_BYTES + B_SLAB_BYTES;   // 24 KiB
 constexpr int GM_THREADS = 320;                            // producer, MMA, 4 epilogue warps, 4 filler warps
 constexpr uint32_t TMEM_COLS = 512;
@@ -374,6 +377,10 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         if (lane == 0) {
             uint32_t slot = 0, acc_iter = 0;
             bool ok = true;
+            // descriptor without the start address: adding (address >> 4) completes it, +16 is the second K=16 half
+            const uint64_t desc0 = smem_desc(0);
+            const uint32_t stage0 = smem_u32(smem);
+            constexpr uint32_t IDESC_N256 = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
             for (uint32_t sidx = 0; ok; sidx++) {
                 const uint32_t d = sidx % SCHED, sph = (sidx / SCHED) & 1u;
                 ok = wait_bounded(smem_u32(&ctrl->sched_full[d]), sph, abort_flag, err, ERR_WAIT_SCHED_FULL);
@@ -394,25 +401,32 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t w = ctrl->step_word[s];
-                    const uint32_t rows = step_rows(w), cols = step_cols(w);
-                    const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
-                    const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
-                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t a_addr = stage0 + s * STAGE_BYTES;
                     const uint32_t b_addr = a_addr + A_SLAB_BYTES;
-                    uint32_t rest = cols;
-                    while (rest) {
-                        const int c0 = __ffs(rest) - 1;
-                        const uint32_t shifted = rest >> c0;
-                        const int len = __ffs(~shifted) - 1;
-                        const uint32_t n = (uint32_t)len * TILE;
-                        const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-                        const uint32_t dcol = tmem_base + buf * ACC_COLS + (uint32_t)c0 * TILE;
-#pragma unroll
-                        for (uint32_t ks = 0; ks < 2; ks++) {
-                            umma_f16(dcol, smem_desc(a_addr + ks * 256u),
-                                     smem_desc(b_addr + (uint32_t)c0 * TILE_BYTES + ks * 256u), idesc, m0, m1, m2, m3);
+                    const uint32_t dbase = tmem_base + buf * ACC_COLS;
+                    if ((w >> 16) == 0xfffu) {
+                        // every row and every column of the macro tile: two instructions with N = 256
+                        const uint64_t da = desc0 + (uint64_t)(a_addr >> 4), db = desc0 + (uint64_t)(b_addr >> 4);
+                        umma_f16(dbase, da, db, IDESC_N256, 0u, 0u, 0u, 0u);
+                        umma_f16(dbase, da + 16u, db + 16u, IDESC_N256, 0u, 0u, 0u, 0u);
+                    } else {
+                        const uint32_t rows = step_rows(w), cols = step_cols(w);
+                        const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
+                        const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
+                        uint32_t rest = cols;
+                        while (rest) {
+                            const int c0 = __ffs(rest) - 1;
+                            const uint32_t shifted = rest >> c0;
+                            const int len = __ffs(~shifted) - 1;
+                            const uint32_t n = (uint32_t)len * TILE;
+                            const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+                            const uint64_t da = desc0 + (uint64_t)(a_addr >> 4);
+                            const uint64_t db = desc0 + (uint64_t)((b_addr + (uint32_t)c0 * TILE_BYTES) >> 4);
+                            const uint32_t dcol = dbase + (uint32_t)c0 * TILE;
+                            umma_f16(dcol, da, db, idesc, m0, m1, m2, m3);
+                            umma_f16(dcol, da + 16u, db + 16u, idesc, m0, m1, m2, m3);
+                            rest &= ~(((1u << len) - 1u) << c0);
                         }
-                        rest &= ~(((1u << len) - 1u) << c0);
                     }
                     umma_commit(smem_u32(&ctrl->empty[s]));
                     slot++;
