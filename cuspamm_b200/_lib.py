@@ -44,6 +44,7 @@ SIGNATURES = {
     "spamm_plan_create": (_i, [_pp, _i, _i, _i, _i, _i, _i]),
     "spamm_plan_destroy": (_i, [_vp]),
     "spamm_upload": (_i, [_vp, _vp, _vp]),
+    "spamm_plan_set_chunk_tiles": (_i, [_vp, _i]),
     "spamm_norms": (_i, [_vp]),
     "spamm_norms_share": (_i, [_vp, _i, _i]),
     "spamm_build_lists": (_i, [_vp, _f]),

@@ -46,7 +46,7 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k
     unsigned int cnt_a = 0, cnt_b = 0;
 
     // one warp per listed tile
-    for (unsigned int t = blockIdx.x * 8 + warp; t < n_list; t += gridDim.x * 8) {
+    for (unsigned int t = sc->tile_begin + blockIdx.x * 8 + warp; t < n_list; t += gridDim.x * 8) {
         const uint32_t id = tile_list[t];
         const int sub = (int)(id & 7u);
         const int64_t slab = (int64_t)((id & 0x7fffffffu) >> 3);

@@ -23,8 +23,11 @@ int record_cuda_error(cudaError_t e, const char *what)
 // Stores a detail message for spamm_last_cuda_error when the failing call is not a CUDA runtime call.
 void record_error_text(const char *text) { g_last_cuda_error = text; }
 
-// The kernels' counters live at the head of the buffer that is cleared before every list build.
+// The kernels' counters live at the head of the buffer that is cleared before every list build: one set for the
+// whole block of rows, or one per chunk of rows when spamm_multiply pipelines the copies with the kernels.
 using DeviceScalars = spamm_list_scalars;
+constexpr int MAX_CHUNKS = 64;
+constexpr size_t CHUNK_TARGET_BYTES = size_t(64) << 20;    // rows of A copied per pipeline step
 
 }  // namespace spamm
 
@@ -53,6 +56,12 @@ struct spamm_plan {
     unsigned long long *d_cv_count = nullptr;   // [count, sum(double)] on the device
     unsigned long long *h_cv = nullptr;         // pinned mirror of the two
     cudaEvent_t ev[8] = {};
+    cudaStream_t stream_d2h = nullptr;  // second stream: copies C chunks out while the next chunk is computed
+    cudaEvent_t ev_chunk[MAX_CHUNKS] = {};
+    int chunk_tiles = 0;                // tile rows per chunk of the pipelined spamm_multiply (multiple of 4)
+    int n_chunks = 1;
+    int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
+    int active_scalars = 1;             // how many scalar sets the last operation used
     bool have_norms = false, have_lists = false, have_pack = false;
     int64_t launches = 0;
 
@@ -106,22 +115,63 @@ size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int read_scalars(spamm_plan *p)
 {
-    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_scalars, p->scalars(), sizeof(DeviceScalars), cudaMemcpyDeviceToHost,
-                                   p->stream));
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_scalars, p->scalars(), sizeof(DeviceScalars) * p->active_scalars,
+                                   cudaMemcpyDeviceToHost, p->stream));
     SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
     return SPAMM_OK;
 }
 
 int status_from_scalars(const spamm_plan *p)
 {
-    if (p->h_scalars->error) return SPAMM_ERR_DEVICE_WAIT;
-    if (p->h_scalars->overflow) return SPAMM_ERR_OVERFLOW;
+    for (int c = 0; c < p->active_scalars; c++) {
+        if (p->h_scalars[c].error) return SPAMM_ERR_DEVICE_WAIT;
+        if (p->h_scalars[c].overflow) return SPAMM_ERR_OVERFLOW;
+    }
     return SPAMM_OK;
+}
+
+int64_t total_survivors(const spamm_plan *p)
+{
+    int64_t s = 0;
+    for (int c = 0; c < p->active_scalars; c++) s += (int64_t)p->h_scalars[c].survivors;
+    return s;
 }
 
 }  // namespace
 
+// (Re)builds the macro-tile orders for the chunk shapes of the pipelined spamm_multiply.
+static int setup_chunk_orders(spamm_plan *p)
+{
+    cudaFree(p->d_order_chunk);
+    cudaFree(p->d_order_last);
+    p->d_order_chunk = p->d_order_last = nullptr;
+    if (p->n_chunks <= 1) return SPAMM_OK;
+    const int last_tiles = p->row_tiles - (p->n_chunks - 1) * p->chunk_tiles;
+    const size_t n_full = (size_t)ceil_div(p->chunk_tiles, MT_R) * p->mj_n;
+    const size_t n_last = (size_t)ceil_div(last_tiles, MT_R) * p->mj_n;
+    std::vector<int32_t> o(n_full > n_last ? n_full : n_last);
+    int st;
+    if ((st = dev_alloc(&p->d_order_chunk, sizeof(int32_t) * n_full))) return st;
+    if ((st = dev_alloc(&p->d_order_last, sizeof(int32_t) * n_last))) return st;
+    spamm_macro_tile_order(p->chunk_tiles, p->n_tiles, o.data());
+    SPAMM_CUDA_TRY(cudaMemcpy(p->d_order_chunk, o.data(), sizeof(int32_t) * n_full, cudaMemcpyHostToDevice));
+    spamm_macro_tile_order(last_tiles, p->n_tiles, o.data());
+    SPAMM_CUDA_TRY(cudaMemcpy(p->d_order_last, o.data(), sizeof(int32_t) * n_last, cudaMemcpyHostToDevice));
+    return SPAMM_OK;
+}
+
 extern "C" {
+
+int spamm_plan_set_chunk_tiles(spamm_plan *p, int tiles)
+{
+    if (!p || tiles <= 0 || tiles % MT_R) return SPAMM_ERR_INVALID;
+    if (p->row_tiles > 0 && ceil_div(p->row_tiles, tiles) > MAX_CHUNKS) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    p->chunk_tiles = tiles;
+    p->n_chunks = p->row_tiles > 0 ? ceil_div(p->row_tiles, tiles) : 1;
+    return setup_chunk_orders(p);
+}
 
 int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin, int row_tile_count, int device)
 {
@@ -153,8 +203,21 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
         spamm_plan_destroy(p);
         return code;
     };
-    if (cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess)
+    if (cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&p->stream_d2h, cudaStreamNonBlocking) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaStreamCreate"));
+    for (auto &e : p->ev_chunk)
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
+            return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
+    {
+        // chunking of the pipelined path: about 64 MiB of A rows per chunk, whole macro-tile rows, at most 64 chunks
+        const size_t row_bytes = sizeof(float) * (size_t)TILE * K;
+        int ct = (int)((CHUNK_TARGET_BYTES + row_bytes - 1) / row_bytes);
+        ct = (ct + MT_R - 1) / MT_R * MT_R;
+        while (p->row_tiles > 0 && ceil_div(p->row_tiles, ct) > MAX_CHUNKS) ct += MT_R;
+        p->chunk_tiles = ct;
+        p->n_chunks = p->row_tiles > 0 ? ceil_div(p->row_tiles, ct) : 1;
+    }
     for (auto &e : p->ev)
         if (cudaEventCreate(&e) != cudaSuccess) return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
     if ((st = dev_alloc(&p->d_a, p->bytes_a()))) return fail(st);
@@ -180,18 +243,19 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
         if (cudaMemcpy(p->d_order, order.data(), p->bytes_step_counts(), cudaMemcpyHostToDevice) != cudaSuccess)
             return fail(record_cuda_error(cudaGetLastError(), "cudaMemcpy(order)"));
     }
-    p->need_a_off = round_up(sizeof(DeviceScalars), 16);
+    if ((st = setup_chunk_orders(p))) return fail(st);
+    p->need_a_off = round_up(sizeof(DeviceScalars) * MAX_CHUNKS, 16);
     p->need_b_off = p->need_a_off + round_up((size_t)p->mi_n * p->k_tiles, 16);
     p->cleared_bytes = p->need_b_off + round_up((size_t)p->k_tiles * p->mj_n, 16);
     if ((st = dev_alloc(&p->d_cleared, p->cleared_bytes))) return fail(st);
     p->cv_scratch_bytes = spamm_count_valid_scratch_bytes(p->row_tiles, p->n_tiles);
     if ((st = dev_alloc(&p->d_cv_scratch, p->cv_scratch_bytes))) return fail(st);
     if ((st = dev_alloc(&p->d_cv_count, 16))) return fail(st);
-    if (cudaMallocHost(reinterpret_cast<void **>(&p->h_scalars), sizeof(DeviceScalars)) != cudaSuccess)
+    if (cudaMallocHost(reinterpret_cast<void **>(&p->h_scalars), sizeof(DeviceScalars) * MAX_CHUNKS) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
     if (cudaMallocHost(reinterpret_cast<void **>(&p->h_cv), 16) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
-    memset(p->h_scalars, 0, sizeof(DeviceScalars));
+    memset(p->h_scalars, 0, sizeof(DeviceScalars) * MAX_CHUNKS);
     if (cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream) != cudaSuccess ||
         cudaStreamSynchronize(p->stream) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMemsetAsync"));
@@ -214,6 +278,10 @@ int spamm_plan_destroy(spamm_plan *p)
     if (p->h_cv) cudaFreeHost(p->h_cv);
     for (auto &e : p->ev)
         if (e) cudaEventDestroy(e);
+    for (auto &e : p->ev_chunk)
+        if (e) cudaEventDestroy(e);
+    cudaFree(p->d_order_chunk); cudaFree(p->d_order_last);
+    if (p->stream_d2h) cudaStreamDestroy(p->stream_d2h);
     if (p->stream) cudaStreamDestroy(p->stream);
     delete p;
     return SPAMM_OK;
@@ -264,6 +332,7 @@ int spamm_build_lists(spamm_plan *p, float tau)
     if (!p->have_norms) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
+    p->active_scalars = 1;
     if (p->row_tiles) {
         int st = spamm_build_lists_dev(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
                                        p->d_list_scratch, p->d_steps, p->d_step_counts, p->d_counts, p->need_a(),
@@ -335,10 +404,13 @@ int spamm_download_c(spamm_plan *p, float *c_rows)
 
 static void fill_stats(spamm_plan *p, spamm_stats *s)
 {
-    s->survivors = (int64_t)p->h_scalars->survivors;
+    s->survivors = total_survivors(p);
     s->tile_products = (int64_t)p->row_tiles * p->k_tiles * p->n_tiles;
-    s->packed_tiles_a = (int64_t)p->h_scalars->packed_a;
-    s->packed_tiles_b = (int64_t)p->h_scalars->packed_b;
+    s->packed_tiles_a = s->packed_tiles_b = 0;
+    for (int c = 0; c < p->active_scalars; c++) {
+        s->packed_tiles_a += (int64_t)p->h_scalars[c].packed_a;
+        s->packed_tiles_b += (int64_t)p->h_scalars[c].packed_b;
+    }
     s->executed_flops = 65536.0 * (double)s->survivors;
 }
 
@@ -402,23 +474,102 @@ int spamm_run_timed(spamm_plan *p, float tau, spamm_stats *stats)
     return status_from_scalars(p);
 }
 
+// One chunk of tile rows [t0, t0+tiles) of the plan's block through norm -> lists -> pack -> multiply, with its own
+// set of counters.  Everything the chunk writes lands where the whole-block path would have put it.
+static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, const int32_t *d_order)
+{
+    const size_t mi0 = (size_t)t0 / MT_R;                 // chunks start on macro-tile rows
+    const size_t mt0 = mi0 * p->mj_n;
+    DeviceScalars *sc = p->scalars() + chunk;
+    float *a = p->d_a + (size_t)t0 * TILE * p->K;
+    float *norm_a = p->d_norm_a + (size_t)t0 * p->k_tiles;
+    int st;
+    if ((st = spamm_norm_map_dev(a, tiles * TILE, p->K, p->K, norm_a, p->stream))) return st;
+    if (chunk > 0) {
+        // the tile list is shared: this chunk's entries follow the previous chunk's
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(&sc->tile_count, &(sc - 1)->tile_count, sizeof(unsigned int),
+                                       cudaMemcpyDeviceToDevice, p->stream));
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(&sc->tile_begin, &(sc - 1)->tile_count, sizeof(unsigned int),
+                                       cudaMemcpyDeviceToDevice, p->stream));
+    }
+    if ((st = spamm_build_lists_dev(norm_a, p->d_norm_b, tiles, p->k_tiles, p->n_tiles, tau, p->d_list_scratch,
+                                    p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
+                                    p->d_counts + (size_t)t0 * p->n_tiles, p->need_a() + mi0 * p->k_tiles, p->need_b(),
+                                    p->d_tile_list, p->d_busy + mt0, sc, p->stream)))
+        return st;
+    uint8_t *half_a = p->d_half_a + mi0 * p->k_tiles * A_SLAB_BYTES;
+    if ((st = spamm_pack_half_dev(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b,
+                                  p->stream)))
+        return st;
+    if ((st = spamm_gated_multiply_dev(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
+                                       d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
+                                       p->d_c + (size_t)t0 * TILE * p->N, p->N, p->stream)))
+        return st;
+    p->launches += 5;
+    return SPAMM_OK;
+}
+
 int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_rows, float tau, spamm_stats *stats)
 {
     if (!p || !a_rows || !b || !c_rows) return SPAMM_ERR_INVALID;
     DeviceGuard guard(p->device);
     int st;
+    if (p->n_chunks <= 1 || p->row_tiles == 0) {
+        // small problem: one pass, phase by phase
+        SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
+        if ((st = spamm_upload(p, a_rows, b))) return st;
+        if ((st = run_with_events(p, tau))) return st;
+        if (p->row_tiles)
+            SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows, p->d_c, p->bytes_c(), cudaMemcpyDeviceToHost, p->stream));
+        SPAMM_CUDA_TRY(cudaEventRecord(p->ev[6], p->stream));
+        if ((st = read_scalars(p))) return st;
+        if (stats) {
+            memset(stats, 0, sizeof(*stats));
+            if ((st = phase_times(p, stats))) return st;
+            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
+            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_d2h, p->ev[4], p->ev[6]));
+            fill_stats(p, stats);
+            stats->steps = sum_step_counts(p, &st);
+            if (st) return st;
+        }
+        return status_from_scalars(p);
+    }
+
+    // Large problem: the copies dominate (PCIe), so they are overlapped with each other and with the kernels.
+    // B goes up first (every C row needs all of it); then the rows of A go up chunk by chunk, each chunk runs the
+    // whole path on the main stream, and its rows of C go down on a second stream while the next chunk goes up.
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
-    if ((st = spamm_upload(p, a_rows, b))) return st;
-    if ((st = run_with_events(p, tau))) return st;
-    if (p->row_tiles)
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows, p->d_c, p->bytes_c(), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream));
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[0], p->stream));
+    if ((st = spamm_norm_map_dev(p->d_b, p->K, p->N, p->N, p->d_norm_b, p->stream))) return st;
+    p->launches++;
+    p->active_scalars = p->n_chunks;
+    for (int c = 0; c < p->n_chunks; c++) {
+        const int t0 = c * p->chunk_tiles;
+        const int tiles = (c == p->n_chunks - 1) ? p->row_tiles - t0 : p->chunk_tiles;
+        const size_t a_off = (size_t)t0 * TILE * p->K, c_off = (size_t)t0 * TILE * p->N;
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a + a_off, a_rows + a_off, sizeof(float) * (size_t)tiles * TILE * p->K,
+                                       cudaMemcpyHostToDevice, p->stream));
+        if ((st = run_chunk(p, c, t0, tiles, tau, c == p->n_chunks - 1 ? p->d_order_last : p->d_order_chunk)))
+            return st;
+        SPAMM_CUDA_TRY(cudaEventRecord(p->ev_chunk[c], p->stream));
+        SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_d2h, p->ev_chunk[c], 0));
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows + c_off, p->d_c + c_off, sizeof(float) * (size_t)tiles * TILE * p->N,
+                                       cudaMemcpyDeviceToHost, p->stream_d2h));
+    }
+    // the main stream ends when the last rows of C have arrived
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev[7], p->stream_d2h));
+    SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev[7], 0));
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[6], p->stream));
+    p->have_norms = p->have_lists = true;
+    p->have_pack = false;       // the per-chunk work lists are not those of a whole-block multiply
     if ((st = read_scalars(p))) return st;
     if (stats) {
         memset(stats, 0, sizeof(*stats));
-        if ((st = phase_times(p, stats))) return st;
+        // the phases interleave with the copies here: only the whole call is timed (spamm_run_timed gives phases)
+        SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_device_total, p->ev[5], p->ev[6]));
         SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
-        SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_d2h, p->ev[4], p->ev[6]));
         fill_stats(p, stats);
         stats->steps = sum_step_counts(p, &st);
         if (st) return st;
@@ -455,7 +606,7 @@ int spamm_get_counts(spamm_plan *p, int32_t *out, int64_t *survivors)
         SPAMM_CUDA_TRY(cudaMemcpyAsync(out, p->d_counts, p->bytes_counts(), cudaMemcpyDeviceToHost, p->stream));
     int st = read_scalars(p);
     if (st) return st;
-    if (survivors) *survivors = (int64_t)p->h_scalars->survivors;
+    if (survivors) *survivors = total_survivors(p);
     return status_from_scalars(p);
 }
 

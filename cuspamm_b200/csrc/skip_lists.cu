@@ -79,8 +79,9 @@ chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ nor
 // Sets bits of a flag byte and returns the bits that were not set before.
 __device__ __forceinline__ uint32_t or_flag_byte(uint8_t *base, int64_t idx, uint32_t bits)
 {
-    unsigned int *w = reinterpret_cast<unsigned int *>(base + (idx & ~int64_t(3)));
-    const unsigned int sh = 8 * (unsigned)(idx & 3);
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(base) + (uintptr_t)idx;
+    unsigned int *w = reinterpret_cast<unsigned int *>(addr & ~uintptr_t(3));
+    const unsigned int sh = 8 * (unsigned)(addr & 3);
     const unsigned int v = bits << sh;
     if ((*reinterpret_cast<volatile unsigned int *>(w) & v) == v) return 0;
     const unsigned int old = atomicOr(w, v);
@@ -265,8 +266,7 @@ extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_
     if (!d_norm_a || !d_norm_b || !d_scratch || !d_steps || !d_step_counts || !d_counts || !d_need_a || !d_need_b ||
         !d_tile_list || !d_busy_list || !d_scalars || row_tiles < 0 || k_tiles < 0 || n_tiles < 0 || k_tiles > 65535)
         return SPAMM_ERR_INVALID;
-    if ((reinterpret_cast<uintptr_t>(d_need_a) & 3) || (reinterpret_cast<uintptr_t>(d_need_b) & 3) ||
-        (reinterpret_cast<uintptr_t>(d_scratch) & 3) || (reinterpret_cast<uintptr_t>(d_scalars) & 7))
+    if ((reinterpret_cast<uintptr_t>(d_scratch) & 3) || (reinterpret_cast<uintptr_t>(d_scalars) & 7))
         return SPAMM_ERR_INVALID;
     const int mi_n = ceil_div(row_tiles, MT_R), mj_n = ceil_div(n_tiles, MT_C), kc_n = ceil_div(k_tiles, 32);
     const int64_t mts = (int64_t)mi_n * mj_n;

@@ -116,6 +116,10 @@ class SpammPlan:
     def n_tiles(self) -> int:
         return self.N // TILE
 
+    def set_chunk_tiles(self, tiles: int) -> None:
+        """Tile rows per chunk of the pipelined `multiply` (multiple of 4)."""
+        check(self._lib.spamm_plan_set_chunk_tiles(self._h, int(tiles)), "spamm_plan_set_chunk_tiles")
+
     # ---- the driver steps
     def upload(self, a_rows=None, b=None) -> None:
         pa = _host_ptr(a_rows, self.rows * self.K * 4) if a_rows is not None else 0

@@ -68,7 +68,8 @@ typedef struct spamm_stats {
  */
 typedef struct spamm_list_scalars {
     unsigned long long survivors;   /* S, written by the list builder */
-    unsigned int tile_count;        /* entries of the list of tiles to convert to half */
+    unsigned int tile_count;        /* end of this problem's entries in the list of tiles to convert to half */
+    unsigned int tile_begin;        /* their beginning: set tile_begin = tile_count = n to append after n earlier entries */
     unsigned int busy_count;        /* entries of the list of macro tiles that have steps */
     unsigned int packed_a;          /* tiles of A converted by the packing kernel */
     unsigned int packed_b;          /* tiles of B converted by the packing kernel */
@@ -143,9 +144,19 @@ int spamm_download_c(spamm_plan *plan, float *c_rows);
  * One call for the whole driver loop body with host matrices in and out (north-star surface:
  * "fp32 host matrices in and out"): upload, norms, lists, pack, multiply, download; blocking.
  * a_rows / c_rows are this plan's row block, b is all of B.  stats may be NULL.
+ * Blocks of more than about 64 MiB of A are processed in chunks of rows so that the upload of the next chunk, the
+ * kernels of the current one and the download of the previous one overlap (use pinned host memory for that); the
+ * phases then interleave and only ms_device_total (the whole call, copies included), ms_h2d (B alone) and the
+ * counts are reported.  After such a call spamm_gated_multiply needs a new spamm_build_lists.
  */
 int spamm_multiply(spamm_plan *plan, const float *a_rows, const float *b, float *c_rows,
                    float tau, spamm_stats *stats);
+
+/*
+ * Tile rows per chunk of the pipelined spamm_multiply (a multiple of 4; at most 64 chunks).  The default is about
+ * 64 MiB of A per chunk.  A value >= the plan's row_tile_count turns the pipelining off.
+ */
+int spamm_plan_set_chunk_tiles(spamm_plan *plan, int tiles);
 
 /* Same as spamm_run but records per-phase events; blocking.  Inputs must already be resident. */
 int spamm_run_timed(spamm_plan *plan, float tau, spamm_stats *stats);
@@ -204,7 +215,9 @@ int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t ld, float *
  *   d_step_counts  [macro tiles] number of steps written
  *   d_counts       [row_tiles][N/32] per-tile list lengths
  *   d_need_a/_b    one byte per A slab of 4 tiles / B slab of 8 tiles, a bit per tile that some step names;
- *                  must be zero on entry
+ *                  zero on entry, or the flags an earlier call on other rows of A left (tiles of B that are flagged
+ *                  already are not listed again); the arrays are accessed in aligned 4-byte words, so keep them
+ *                  padded to a multiple of 4 bytes
  *   d_tile_list    every named tile once: bit 31 = tile of B, bits 3-30 = slab index, bits 0-2 = tile in the slab;
  *                  room for (4*ceil(row_tiles/4) + 8*ceil(n_tiles/8)) * (K/32) entries
  *   d_busy_list    the macro tiles with at least one step, in no particular order; room for all macro tiles
@@ -222,7 +235,7 @@ int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_
  *     byte offset of element (o, kk) = (o/8)*512 + (kk/8)*128 + (o%8)*16 + (kk%8)*2,
  * o = row of an A tile / column of a B tile, kk = the index that is summed over.  A tiles are grouped
  * 4 (rows) to a slab, slabs ordered [row group][k]; B tiles 8 (columns) to a slab, slabs ordered [k][column group].
- * d_tile_list and d_scalars->tile_count come from spamm_build_lists_dev.
+ * d_tile_list and d_scalars->tile_begin / tile_count come from spamm_build_lists_dev.
  */
 int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
                         const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,

@@ -113,3 +113,30 @@ def test_count_valid_and_tuner(oracle):
     assert it_g == it_o
     assert rate_g == rate_o
     assert abs(tau_g - tau_o) <= 1e-6 * abs(tau_o)
+
+
+@pytest.mark.parametrize("chunk_tiles", [4, 8, 12])
+def test_pipelined_host_to_host_multiply(oracle, chunk_tiles):
+    """spamm_multiply with the rows of A processed in chunks (uploads, kernels and downloads overlapped): same
+    result, same lists as the one-pass path; the last chunk is shorter than the others for 12."""
+    from cuspamm_b200 import SpammPlan
+
+    n = 640                                      # 20 tile rows
+    A = signed_decay(n, 0.03, seed=41)
+    B = signed_decay(n, 0.04, seed=42)
+    tau = 0.2
+    Cref, S, nA, nB, counts = oracle.spamm(A, B, tau, want_maps=True)
+    with SpammPlan(n, n, n) as p:
+        p.set_chunk_tiles(chunk_tiles)
+        for _ in range(2):                       # twice: flags and lists of the first call must not leak
+            C, st = p.multiply(A, B, tau)
+            assert st["survivors"] == S
+            assert rel_fro(C, Cref) <= C_TOL
+        got_counts, got_s = p.counts()
+        assert got_s == S and np.array_equal(got_counts, counts)
+        assert np.array_equal(p.norm_a().view(np.uint32), nA.view(np.uint32))
+        offs, kidx = p.lists()
+        _, o2, k2 = oracle.lists(nA, nB, tau)
+        assert np.array_equal(offs, o2) and np.array_equal(kidx, k2)
+        assert st["packed_tiles_a"] == int((nA[:, :, None] * nB[None] >= np.float32(tau)).any(axis=2).sum())
+        assert st["packed_tiles_b"] == int((nA[:, :, None] * nB[None] >= np.float32(tau)).any(axis=0).sum())
