@@ -1,0 +1,138 @@
+"""The benchmark configurations (BASELINE.json) on the GPU: exact comparison with the CPU checker where it
+finishes in seconds, and size-independent properties at the full sizes (survivor counts against the checker's
+count on the same norm maps, dense limit against a float matrix product of the half-rounded inputs, row blocks
+that tile the result, a second call that reproduces the first bit for bit)."""
+import numpy as np
+import pytest
+
+from conftest import rel_fro
+
+pytestmark = pytest.mark.gpu
+C_TOL = 1e-3
+
+
+def full_check(oracle, A, B, tau):
+    from cuspamm_b200 import SpammPlan
+
+    n = A.shape[0]
+    C_ref, S, nA, nB, counts = oracle.spamm(A, B, tau, want_maps=True)
+    with SpammPlan(n, A.shape[1], B.shape[1]) as p:
+        p.upload(A, B)
+        p.run(tau)
+        p.sync()
+        C = p.download_c()
+        got_counts, got_s = p.counts()
+        assert np.array_equal(p.norm_a().view(np.uint32), nA.view(np.uint32))
+        assert np.array_equal(p.norm_b().view(np.uint32), nB.view(np.uint32))
+    assert got_s == S and np.array_equal(got_counts, counts)
+    err = rel_fro(C, C_ref)
+    assert err <= C_TOL, err
+    return S, err
+
+
+@pytest.mark.parametrize("tau", [1e-10, 1e-6, 1e-4, 1e-2])
+def test_config2_exponential_decay_sweep(oracle, tau):
+    """Config 2 family at N=4096: a_ij = +-exp(-0.1|i-j|), independent seeds, the sweep's non-zero thresholds."""
+    from cuspamm_b200 import gen_signed_exp
+
+    n = 4096
+    A, B = gen_signed_exp(0.1, 1, n, n), gen_signed_exp(0.1, 2, n, n)
+    S, err = full_check(oracle, A, B, tau)
+    assert 0 < S < (n // 32) ** 3 // 20
+    assert err < 1e-5
+
+
+def test_config2_dense_limit_tau_zero():
+    """tau = 0 keeps every product (0 >= 0 included): C is the product of the half-rounded inputs."""
+    import torch
+
+    from cuspamm_b200 import SpammPlan, gen_signed_exp
+
+    n = 4096
+    A, B = gen_signed_exp(0.1, 1, n, n), gen_signed_exp(0.1, 2, n, n)
+    with SpammPlan(n, n, n) as p:
+        C, st = p.multiply(A, B, 0.0)
+    assert st["survivors"] == (n // 32) ** 3
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = (torch.from_numpy(A).cuda().half().float() @ torch.from_numpy(B).cuda().half().float()).cpu().numpy()
+    assert rel_fro(C, ref) < 1e-5
+
+
+def test_config3_algebraic_decay(oracle):
+    """Config 3 family: a_ij = u_ij/(|i-j|^2+1), u in [-1,1); exact check at N=4096."""
+    from cuspamm_b200 import gen_uniform_alg
+
+    n = 4096
+    A, B = gen_uniform_alg(3, n, n), gen_uniform_alg(4, n, n)
+    S, err = full_check(oracle, A, B, 1e-6)
+    assert err < 1e-5
+
+
+def test_config4_lattice(oracle):
+    """Config 4 family on a 16^3 lattice (N=4096): symmetric, list lengths spread over a wide range."""
+    from cuspamm_b200 import gen_lattice
+
+    A = gen_lattice(16, 7)
+    assert np.array_equal(A, A.T)
+    S, err = full_check(oracle, A, A.copy(), 1e-8)
+    assert err < 1e-5
+
+
+def test_full_size_properties_n16384(oracle):
+    """N=16384 (the headline size): counts against the checker's count on the library's own (bit-checked) norm maps,
+    one row block against the checker, two half-height plans against the full one, and a repeat of the run."""
+    from cuspamm_b200 import SpammPlan, gen_signed_exp
+
+    n, tau = 16384, 1e-6
+    A, B = gen_signed_exp(0.1, 1, n, n), gen_signed_exp(0.1, 2, n, n)
+    T = n // 32
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        p.run(tau)
+        p.sync()
+        C = p.download_c()
+        nA, nB = p.norm_a(), p.norm_b()
+        counts, S = p.counts()
+        p.run(tau)
+        p.sync()
+        assert np.array_equal(p.download_c(), C)            # same lists, same order of accumulation
+    # norm maps: two tile rows bit for bit (the full map is checked at smaller sizes)
+    assert np.array_equal(nA[40:42].view(np.uint32), oracle.norm_map(A[40 * 32:42 * 32]).view(np.uint32))
+    assert np.array_equal(nB[500:502].view(np.uint32), oracle.norm_map(B[500 * 32:502 * 32]).view(np.uint32))
+    c_counts, _, _ = oracle.lists(nA, nB, tau)
+    assert np.array_equal(counts, c_counts) and S == int(c_counts.sum())
+    assert S == 55344                                        # recorded with the first verified run of this workload
+    # a block of 8 tile rows against the checker
+    C_blk, S_blk = oracle.spamm(A, B, tau, row_begin=200, row_count=8)
+    assert S_blk == int(counts[200:208].sum())
+    assert rel_fro(C[200 * 32:208 * 32], C_blk) <= C_TOL
+    # everything outside the band of surviving tiles is exactly zero
+    Ct = np.abs(C).reshape(T, 32, T, 32).max(axis=(1, 3))
+    assert not Ct[counts == 0].any()
+    # the reference's row split: two plans, each half of the tile rows, reproduce the full C
+    parts = []
+    for b0 in (0, T // 2):
+        with SpammPlan(n, n, n, b0, T // 2) as q:
+            q.upload(np.ascontiguousarray(A[b0 * 32:(b0 + T // 2) * 32]), B)
+            q.run(tau)
+            q.sync()
+            parts.append(q.download_c())
+    assert rel_fro(np.vstack(parts), C) < 1e-6
+
+
+def test_config5_dense_uniform_rows_sample():
+    """Config 5 (dense uniform, tau=0) at N=8192: every product executed, rows checked against a float product."""
+    import torch
+
+    from cuspamm_b200 import SpammPlan, gen_uniform
+
+    n = 8192
+    A, B = gen_uniform(5, n, n), gen_uniform(6, n, n)
+    with SpammPlan(n, n, n) as p:
+        C, st = p.multiply(A, B, 0.0)
+    assert st["survivors"] == (n // 32) ** 3
+    torch.backends.cuda.matmul.allow_tf32 = False
+    Bh = torch.from_numpy(B).cuda().half().float()
+    for r0 in (0, 4000, 8192 - 256):
+        ref = (torch.from_numpy(A[r0:r0 + 256]).cuda().half().float() @ Bh).cpu().numpy()
+        assert rel_fro(C[r0:r0 + 256], ref) < 1e-5
