@@ -216,13 +216,17 @@ def run_ours(args):
 
     stream = plan.torch_stream()
 
+    issue_ms = [0.0]
+
     def timed(fn, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
+        t_issue = time.perf_counter()
         for _ in range(steps):
             fn()
         e1.record(stream)
+        issue_ms[0] = (time.perf_counter() - t_issue) * 1e3 / steps     # host time to issue one step
         torch.cuda.synchronize()
         barrier()
         ms = e0.elapsed_time(e1) / steps
@@ -243,6 +247,7 @@ def run_ours(args):
         sampler.start()
     ms_step = timed(lambda: sh.run(tau), args.steps)
     clocks = sampler.stop() if sampler else None
+    host_issue_ms = issue_ms[0]
     launches = plan.kernel_launches() - launches0
     sh.sync()
 
@@ -313,6 +318,7 @@ def run_ours(args):
         "e2e": {"value": 65536.0 * S / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": 8 * n * n, "d2h_bytes_per_step": 4 * n * n, "steps": e2e_steps},
         "gpu_launches": launches,
+        "host_issue_ms_per_step": host_issue_ms,
         "clocks": clocks,
     }
     if phase is not None:

@@ -74,6 +74,24 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     return LIB_PATH
 
 
+def build_driver(verbose: bool = False) -> Path:
+    """Builds the command-line driver `spamm_main` (same shape as the reference's `main`) against libspamm.so."""
+    build_library()
+    out = PKG_DIR / "spamm_main"
+    src = CSRC / "spamm_main.cpp"
+    if not _stale(out, [src, LIB_PATH] + HEADERS):
+        return out
+    cmd = [_nvcc(), "-O2", "-std=c++17", str(src), "-o", str(out), f"-L{PKG_DIR}", "-lspamm", "-lcudart",
+           "-Xlinker", f"-rpath={PKG_DIR}", "-Xlinker", "-rpath=$ORIGIN"]
+    if verbose:
+        print(" ".join(cmd), file=sys.stderr)
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"driver build failed:\n{r.stdout}")
+    return out
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
     print(path)
+    print(build_driver(verbose=True))

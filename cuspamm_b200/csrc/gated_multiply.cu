@@ -24,16 +24,24 @@
 
 namespace spamm {
 
+// A stage of the ring holds the operands of up to SPS consecutive steps of one macro tile.  The thread that issues the
+// multiplies pays a fixed price per stage (barrier wait, commit) and about 110 cycles per tcgen05.mma, against 128
+// cycles of tensor-pipe time for an N=256 instruction, so several steps share one wait and one commit.
+#ifndef SPAMM_SPS
+#define SPAMM_SPS 2
+#endif
+constexpr int SPS = SPAMM_SPS;
+constexpr int STAGE_BYTES = SPS * (A_SLAB_BYTES + B_SLAB_BYTES);   // 24 KiB per step
 #ifndef SPAMM_STAGES
-#define SPAMM_STAGES 6
+#define SPAMM_STAGES (8 / SPAMM_SPS)
 #endif
 constexpr int STAGES = SPAMM_STAGES;
-constexpr int STAGE_BYTES = A_SLAB_BYTES + B_SLAB_BYTES;   // 24 KiB
+constexpr int STEP_BATCH = 32 / SPS * SPS;                   // steps fetched per warp-wide read of the list
 constexpr int GM_THREADS = 320;                            // producer, MMA, 4 epilogue warps, 4 filler warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = MT_C * TILE;                  // 256
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
-constexpr int SMEM_CTRL_BYTES = 384;
+constexpr int SMEM_CTRL_BYTES = 512;
 constexpr int SCHED = 4;                                    // depth of the ring of scheduled macro tiles
 constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 128;
 
@@ -49,7 +57,7 @@ struct Ctrl {
     uint32_t filler_base[2];
     int32_t tile_slot[SCHED];
     int32_t tile_cnt[SCHED];
-    uint32_t step_word[STAGES];
+    uint32_t step_word[STAGES][SPS];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -319,41 +327,69 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             const uint32_t *list = steps + (int64_t)mt * cap;
             const uint8_t *a_base = half_a + (int64_t)mi * k_tiles * A_SLAB_BYTES;
             const uint8_t *b_base = half_b + (int64_t)mj * B_SLAB_BYTES;
-            uint32_t next = (lane < cnt) ? __ldg(list + lane) : 0u;
-            for (int i0 = 0; i0 < cnt && ok; i0 += 32) {
+            uint32_t next = (lane < STEP_BATCH && lane < cnt) ? __ldg(list + lane) : 0u;
+            for (int i0 = 0; i0 < cnt && ok; i0 += STEP_BATCH) {
                 const uint32_t mine = next;
-                // fetch the following 32 steps while these are being issued
-                next = (i0 + 32 + lane < cnt) ? __ldg(list + i0 + 32 + lane) : 0u;
-                const int nb = min(32, cnt - i0);
-                for (int j = 0; j < nb; j++) {
-                    const uint32_t w = __shfl_sync(0xffffffffu, mine, j);
+                // fetch the following batch of steps while these are being issued
+                next = (lane < STEP_BATCH && i0 + STEP_BATCH + lane < cnt) ? __ldg(list + i0 + STEP_BATCH + lane) : 0u;
+                const int nb = min(STEP_BATCH, cnt - i0);
+                for (int j = 0; j < nb; j += SPS) {
+                    uint32_t w[SPS];
+#pragma unroll
+                    for (int t = 0; t < SPS; t++) {
+                        w[t] = __shfl_sync(0xffffffffu, mine, (j + t) & 31);
+                        if (j + t >= nb) w[t] = 0u;              // a step word is never zero (its row set is not empty)
+                    }
                     if (lane == 0) {
                         const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
                         ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, ERR_WAIT_EMPTY);
                         if (ok) {
-                            const uint32_t k = step_k(w), rows = step_rows(w), cols = step_cols(w);
                             const uint32_t bar = smem_u32(&ctrl->full[s]);
-                            const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
-                            const uint32_t b_dst = a_dst + A_SLAB_BYTES;
-                            ctrl->step_word[s] = w;
-                            mbar_arrive_expect_tx(bar, (__popc(rows) + __popc(cols)) * TILE_BYTES);
-                            const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
-                            if (rows == 0xfu) {
-                                bulk_g2s(a_dst, a_src, A_SLAB_BYTES, bar);
-                            } else {
+                            const uint32_t a_stage = smem_u32(smem + s * STAGE_BYTES);
+                            const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+                            uint32_t tiles = 0;
 #pragma unroll
-                                for (int q = 0; q < MT_R; q++)
-                                    if ((rows >> q) & 1u)
-                                        bulk_g2s(a_dst + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
+                            for (int t = 0; t < SPS; t++) {
+                                ctrl->step_word[s][t] = w[t];
+                                tiles += __popc(w[t] >> 16);       // rows and columns named by the step
                             }
-                            const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
-                            uint32_t rest = cols;
-                            while (rest) {
-                                const int c0 = __ffs(rest) - 1;
-                                const uint32_t shifted = rest >> c0;
-                                const int len = __ffs(~shifted) - 1;   // run of ones starting at c0
-                                bulk_g2s(b_dst + c0 * TILE_BYTES, b_src + c0 * TILE_BYTES, len * TILE_BYTES, bar);
-                                rest &= ~(((1u << len) - 1u) << c0);
+                            mbar_arrive_expect_tx(bar, tiles * TILE_BYTES);
+                            bool a_done = false;
+                            if (SPS >= 2 && (w[0] >> 16) == 0xfffu && (w[1] >> 16) == 0xfffu &&
+                                step_k(w[1]) == step_k(w[0]) + 1u) {
+                                // two full steps with consecutive k: their A slabs are neighbours in memory
+                                bulk_g2s(a_stage, a_base + (int64_t)step_k(w[0]) * A_SLAB_BYTES, 2 * A_SLAB_BYTES, bar);
+                                a_done = true;
+                            }
+#pragma unroll
+                            for (int t = 0; t < SPS; t++) {
+                                if (w[t] == 0u) break;
+                                const uint32_t k = step_k(w[t]), rows = step_rows(w[t]), cols = step_cols(w[t]);
+                                const uint32_t a_dst = a_stage + t * A_SLAB_BYTES;
+                                const uint32_t b_dst = b_stage + t * B_SLAB_BYTES;
+                                const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
+                                const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
+                                if (a_done && t < 2) {
+                                } else if (rows == 0xfu) {
+                                    bulk_g2s(a_dst, a_src, A_SLAB_BYTES, bar);
+                                } else {
+#pragma unroll
+                                    for (int q = 0; q < MT_R; q++)
+                                        if ((rows >> q) & 1u)
+                                            bulk_g2s(a_dst + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
+                                }
+                                if (cols == 0xffu) {
+                                    bulk_g2s(b_dst, b_src, B_SLAB_BYTES, bar);
+                                } else {
+                                    uint32_t rest = cols;
+                                    while (rest) {
+                                        const int c0 = __ffs(rest) - 1;
+                                        const uint32_t shifted = rest >> c0;
+                                        const int len = __ffs(~shifted) - 1;   // run of ones starting at c0
+                                        bulk_g2s(b_dst + c0 * TILE_BYTES, b_src + c0 * TILE_BYTES, len * TILE_BYTES, bar);
+                                        rest &= ~(((1u << len) - 1u) << c0);
+                                    }
+                                }
                             }
                             slot++;
                         }
@@ -395,37 +431,44 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                                   ERR_WAIT_TMEM_EMPTY);
                 if (!ok) break;
                 tc_fence_after();
-                for (int i = 0; i < cnt; i++) {
+                const uint32_t dbase = tmem_base + buf * ACC_COLS;
+                const int n_groups = (cnt + SPS - 1) / SPS;
+                for (int g = 0; g < n_groups; g++) {
                     const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
                     ok = wait_bounded(smem_u32(&ctrl->full[s]), ph, abort_flag, err, ERR_WAIT_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t w = ctrl->step_word[s];
-                    const uint32_t a_addr = stage0 + s * STAGE_BYTES;
-                    const uint32_t b_addr = a_addr + A_SLAB_BYTES;
-                    const uint32_t dbase = tmem_base + buf * ACC_COLS;
-                    if ((w >> 16) == 0xfffu) {
-                        // every row and every column of the macro tile: two instructions with N = 256
-                        const uint64_t da = desc0 + (uint64_t)(a_addr >> 4), db = desc0 + (uint64_t)(b_addr >> 4);
-                        umma_f16(dbase, da, db, IDESC_N256, 0u, 0u, 0u, 0u);
-                        umma_f16(dbase, da + 16u, db + 16u, IDESC_N256, 0u, 0u, 0u, 0u);
-                    } else {
-                        const uint32_t rows = step_rows(w), cols = step_cols(w);
-                        const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
-                        const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
-                        uint32_t rest = cols;
-                        while (rest) {
-                            const int c0 = __ffs(rest) - 1;
-                            const uint32_t shifted = rest >> c0;
-                            const int len = __ffs(~shifted) - 1;
-                            const uint32_t n = (uint32_t)len * TILE;
-                            const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-                            const uint64_t da = desc0 + (uint64_t)(a_addr >> 4);
-                            const uint64_t db = desc0 + (uint64_t)((b_addr + (uint32_t)c0 * TILE_BYTES) >> 4);
-                            const uint32_t dcol = dbase + (uint32_t)c0 * TILE;
-                            umma_f16(dcol, da, db, idesc, m0, m1, m2, m3);
-                            umma_f16(dcol, da + 16u, db + 16u, idesc, m0, m1, m2, m3);
-                            rest &= ~(((1u << len) - 1u) << c0);
+                    const uint32_t a_stage = stage0 + s * STAGE_BYTES;
+                    const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+#pragma unroll
+                    for (int t = 0; t < SPS; t++) {
+                        const uint32_t w = ctrl->step_word[s][t];
+                        if (w == 0u) break;
+                        const uint32_t a_addr = a_stage + t * A_SLAB_BYTES;
+                        const uint32_t b_addr = b_stage + t * B_SLAB_BYTES;
+                        if ((w >> 16) == 0xfffu) {
+                            // every row and every column of the macro tile: two instructions with N = 256
+                            const uint64_t da = desc0 + (uint64_t)(a_addr >> 4), db = desc0 + (uint64_t)(b_addr >> 4);
+                            umma_f16(dbase, da, db, IDESC_N256, 0u, 0u, 0u, 0u);
+                            umma_f16(dbase, da + 16u, db + 16u, IDESC_N256, 0u, 0u, 0u, 0u);
+                        } else {
+                            const uint32_t rows = step_rows(w), cols = step_cols(w);
+                            const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
+                            const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
+                            uint32_t rest = cols;
+                            while (rest) {
+                                const int c0 = __ffs(rest) - 1;
+                                const uint32_t shifted = rest >> c0;
+                                const int len = __ffs(~shifted) - 1;
+                                const uint32_t n = (uint32_t)len * TILE;
+                                const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+                                const uint64_t da = desc0 + (uint64_t)(a_addr >> 4);
+                                const uint64_t db = desc0 + (uint64_t)((b_addr + (uint32_t)c0 * TILE_BYTES) >> 4);
+                                const uint32_t dcol = dbase + (uint32_t)c0 * TILE;
+                                umma_f16(dcol, da, db, idesc, m0, m1, m2, m3);
+                                umma_f16(dcol, da + 16u, db + 16u, idesc, m0, m1, m2, m3);
+                                rest &= ~(((1u << len) - 1u) << c0);
+                            }
                         }
                     }
                     umma_commit(smem_u32(&ctrl->empty[s]));
@@ -566,19 +609,21 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
     if (n_mt == 0) return SPAMM_OK;
     if (n_mt > 0x3fffffffLL) return SPAMM_ERR_UNSUPPORTED;
 
-    static thread_local int configured_device = -1;
-    static thread_local int sm_count = 0;
+    // per device, once: the kernel's shared-memory limit and the SM count (a process may drive several GPUs in turn)
+    static int sm_count_of[64] = {};
     int dev = 0;
     SPAMM_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_device != dev) {
-        cudaDeviceProp prop;
-        SPAMM_CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
-        if (prop.major != 10) return SPAMM_ERR_UNSUPPORTED;
+    if (dev < 0 || dev >= 64) return SPAMM_ERR_UNSUPPORTED;
+    if (sm_count_of[dev] == 0) {
+        int major = 0, sms = 0;
+        SPAMM_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        SPAMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (major != 10) return SPAMM_ERR_UNSUPPORTED;
         SPAMM_CUDA_TRY(cudaFuncSetAttribute(gated_multiply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             GM_SMEM_BYTES));
-        sm_count = prop.multiProcessorCount;
-        configured_device = dev;
+        sm_count_of[dev] = sms;
     }
+    const int sm_count = sm_count_of[dev];
     // the two work counters start from zero at every launch
     SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 2 * sizeof(unsigned int), (cudaStream_t)stream));
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);

@@ -186,9 +186,9 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     if (device < 0 || device >= ndev) return SPAMM_ERR_INVALID;
     DeviceGuard guard(device);
     if (!guard.ok) return record_cuda_error(cudaGetLastError(), "cudaSetDevice");
-    cudaDeviceProp prop;
-    SPAMM_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
-    if (prop.major != 10) return SPAMM_ERR_UNSUPPORTED;
+    int cc_major = 0;
+    SPAMM_CUDA_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
+    if (cc_major != 10) return SPAMM_ERR_UNSUPPORTED;
 
     spamm_plan *p = new (std::nothrow) spamm_plan();
     if (!p) return SPAMM_ERR_ALLOC;

@@ -279,6 +279,8 @@ class ShardedSpamm:
         k_tiles = K // TILE
         # equal shares of B's tile rows when they divide evenly, otherwise every rank computes the whole map
         self._share = (k_tiles // self.world) if (self.world > 1 and k_tiles % self.world == 0) else None
+        self._nb = self._mine = self._stream = None
+        self._nccl = False
 
     def _on_stream(self):
         ts = getattr(self.plan, "torch_stream", None)
@@ -301,14 +303,19 @@ class ShardedSpamm:
             self.plan.norms()
         else:
             self.plan.norms_share(self.rank * self._share, self._share)
-            with self._on_stream():
-                nb = self.plan.as_tensor(BUF_NORM_B)
-                mine = nb[self.rank * self._share:(self.rank + 1) * self._share]
-                if self._dist.get_backend(self.group) == "nccl":
+            if self._nb is None:      # views and stream context are built once: this runs every step
+                self._nb = self.plan.as_tensor(BUF_NORM_B)
+                self._mine = self._nb[self.rank * self._share:(self.rank + 1) * self._share]
+                self._nccl = self._dist.get_backend(self.group) == "nccl"
+                ts = getattr(self.plan, "torch_stream", None)
+                self._stream = ts() if ts is not None else None
+            nb, mine = self._nb, self._mine
+            if self._nccl:
+                with self._torch.cuda.stream(self._stream):
                     self._dist.all_gather_into_tensor(nb, mine, group=self.group)   # in place
-                else:
-                    parts = [nb[r * self._share:(r + 1) * self._share] for r in range(self.world)]
-                    self._dist.all_gather(parts, mine.clone(), group=self.group)
+            else:
+                parts = [nb[r * self._share:(r + 1) * self._share] for r in range(self.world)]
+                self._dist.all_gather(parts, mine.clone(), group=self.group)
         self.plan.build_lists(tau)
         self.plan.pack()
         self.plan.gated_multiply()
