@@ -263,6 +263,14 @@ def run_ours(args):
         phase = {k: acc[k] / reps for k in ("ms_norm", "ms_lists", "ms_pack", "ms_multiply", "ms_device_total")}
         phase.update({k: int(st[k]) for k in ("steps", "packed_tiles_a", "packed_tiles_b")})
 
+    elif sh._share is not None:
+        acc = {}
+        reps = max(3, min(args.steps, 10))
+        for _ in range(reps):
+            for k, v in sh.run_timed(tau).items():
+                acc[k] = acc.get(k, 0.0) + v
+        phase = {k: v / reps for k, v in acc.items()}      # rank 0's view
+
     # ---- end to end through the public call with host buffers (pinned): H2D + device + gather + D2H
     e2e_steps = max(1, min(args.steps, 3))
     c_t, c_np = pinned((n, n)) if rank == 0 else (None, None)
@@ -321,7 +329,9 @@ def run_ours(args):
         "host_issue_ms_per_step": host_issue_ms,
         "clocks": clocks,
     }
-    if phase is not None:
+    if phase is not None and world > 1:
+        line["phases_ms_rank0"] = phase
+    if phase is not None and world == 1:
         norm_bytes = 8.0 * n * n   # every float of A and of B read once
         achieved = norm_bytes / (phase["ms_norm"] * 1e-3) / 1e9
         ratio = read_traffic_ratio()

@@ -47,6 +47,8 @@ SIGNATURES = {
     "spamm_plan_set_chunk_tiles": (_i, [_vp, _i]),
     "spamm_norms": (_i, [_vp]),
     "spamm_norms_share": (_i, [_vp, _i, _i]),
+    "spamm_norm_b_share": (_i, [_vp, _i, _i]),
+    "spamm_norm_a": (_i, [_vp]),
     "spamm_build_lists": (_i, [_vp, _f]),
     "spamm_pack": (_i, [_vp]),
     "spamm_gated_multiply": (_i, [_vp]),

@@ -298,26 +298,40 @@ int spamm_upload(spamm_plan *p, const float *a_rows, const float *b)
     return SPAMM_OK;
 }
 
-int spamm_norms_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
+int spamm_norm_b_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
 {
     if (!p || b_tile_begin < 0 || b_tile_count < 0 || b_tile_begin + (int64_t)b_tile_count > p->k_tiles)
         return SPAMM_ERR_INVALID;
     DeviceGuard guard(p->device);
-    int st;
     if (b_tile_count) {
-        st = spamm_norm_map_dev(p->d_b + (size_t)b_tile_begin * TILE * p->N, b_tile_count * TILE, p->N, p->N,
-                                p->d_norm_b + (size_t)b_tile_begin * p->n_tiles, p->stream);
+        int st = spamm_norm_map_dev(p->d_b + (size_t)b_tile_begin * TILE * p->N, b_tile_count * TILE, p->N, p->N,
+                                    p->d_norm_b + (size_t)b_tile_begin * p->n_tiles, p->stream);
         if (st) return st;
         p->launches++;
     }
-    if (p->row_tiles) {
-        st = spamm_norm_map_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->stream);
-        if (st) return st;
-        p->launches++;
-    }
-    p->have_norms = true;
     p->have_lists = p->have_pack = false;
     return SPAMM_OK;
+}
+
+int spamm_norm_a(spamm_plan *p)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    if (p->row_tiles) {
+        int st = spamm_norm_map_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->stream);
+        if (st) return st;
+        p->launches++;
+    }
+    p->have_norms = true;       // the caller answers for B's map (spamm_norm_b_share + its exchange)
+    p->have_lists = p->have_pack = false;
+    return SPAMM_OK;
+}
+
+int spamm_norms_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
+{
+    int st = spamm_norm_b_share(p, b_tile_begin, b_tile_count);
+    if (st) return st;
+    return spamm_norm_a(p);
 }
 
 int spamm_norms(spamm_plan *p)

@@ -132,6 +132,12 @@ class SpammPlan:
     def norms_share(self, b_tile_begin: int, b_tile_count: int) -> None:
         check(self._lib.spamm_norms_share(self._h, b_tile_begin, b_tile_count), "spamm_norms_share")
 
+    def norm_b_share(self, b_tile_begin: int, b_tile_count: int) -> None:
+        check(self._lib.spamm_norm_b_share(self._h, b_tile_begin, b_tile_count), "spamm_norm_b_share")
+
+    def compute_norm_a(self) -> None:
+        check(self._lib.spamm_norm_a(self._h), "spamm_norm_a")
+
     def build_lists(self, tau: float) -> None:
         check(self._lib.spamm_build_lists(self._h, float(tau)), "spamm_build_lists")
 
@@ -279,7 +285,7 @@ class ShardedSpamm:
         k_tiles = K // TILE
         # equal shares of B's tile rows when they divide evenly, otherwise every rank computes the whole map
         self._share = (k_tiles // self.world) if (self.world > 1 and k_tiles % self.world == 0) else None
-        self._nb = self._mine = self._stream = None
+        self._nb = self._mine = self._stream = self._side = None
         self._nccl = False
 
     def _on_stream(self):
@@ -302,23 +308,58 @@ class ShardedSpamm:
         if self._share is None:
             self.plan.norms()
         else:
-            self.plan.norms_share(self.rank * self._share, self._share)
-            if self._nb is None:      # views and stream context are built once: this runs every step
+            if self._nb is None:      # views and streams are built once: this runs every step
                 self._nb = self.plan.as_tensor(BUF_NORM_B)
                 self._mine = self._nb[self.rank * self._share:(self.rank + 1) * self._share]
                 self._nccl = self._dist.get_backend(self.group) == "nccl"
                 ts = getattr(self.plan, "torch_stream", None)
                 self._stream = ts() if ts is not None else None
+                self._side = self._torch.cuda.Stream(priority=-1) if self._nccl else None   # its blocks go first
             nb, mine = self._nb, self._mine
             if self._nccl:
-                with self._torch.cuda.stream(self._stream):
+                # this rank's share of B's map first, then its exchange on a side stream while A's map is computed
+                self.plan.norm_b_share(self.rank * self._share, self._share)
+                self._side.wait_stream(self._stream)
+                with self._torch.cuda.stream(self._side):
                     self._dist.all_gather_into_tensor(nb, mine, group=self.group)   # in place
+                self.plan.compute_norm_a()
+                self._stream.wait_stream(self._side)
             else:
+                self.plan.norms_share(self.rank * self._share, self._share)
                 parts = [nb[r * self._share:(r + 1) * self._share] for r in range(self.world)]
                 self._dist.all_gather(parts, mine.clone(), group=self.group)
         self.plan.build_lists(tau)
         self.plan.pack()
         self.plan.gated_multiply()
+
+    def run_timed(self, tau: float) -> dict:
+        """One `run` with CUDA events between its parts (this rank's view, milliseconds); blocking."""
+        torch = self._torch
+        stream = self.plan.torch_stream()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev[0].record(stream)
+        if self._share is None:
+            self.plan.norms()
+            ev[1].record(stream)
+        else:
+            self.plan.norms_share(self.rank * self._share, self._share)
+            ev[1].record(stream)
+            nb = self.plan.as_tensor(BUF_NORM_B)
+            mine = nb[self.rank * self._share:(self.rank + 1) * self._share]
+            with torch.cuda.stream(stream):
+                self._dist.all_gather_into_tensor(nb, mine, group=self.group)
+        ev[2].record(stream)
+        self.plan.build_lists(tau)
+        ev[3].record(stream)
+        self.plan.pack()
+        ev[4].record(stream)
+        self.plan.gated_multiply()
+        ev[5].record(stream)
+        self.plan.sync()
+        names = ["ms_norm", "ms_allgather", "ms_lists", "ms_pack", "ms_multiply"]
+        out = {n: ev[i].elapsed_time(ev[i + 1]) for i, n in enumerate(names)}
+        out["ms_device_total"] = ev[0].elapsed_time(ev[5])
+        return out
 
     def sync(self) -> None:
         self.plan.sync()

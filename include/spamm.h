@@ -133,6 +133,9 @@ int spamm_run(spamm_plan *plan, float tau);
  * before spamm_build_lists.  The reference recomputes the whole map of B on every device (cuSpAMM.cu:486).
  */
 int spamm_norms_share(spamm_plan *plan, int b_tile_begin, int b_tile_count);
+/* The two halves of spamm_norms_share, so that the exchange of B's shares can run while A's map is computed. */
+int spamm_norm_b_share(spamm_plan *plan, int b_tile_begin, int b_tile_count);
+int spamm_norm_a(spamm_plan *plan);
 
 /* Waits for the plan's stream, then reports a device-side wait that ran out (SPAMM_ERR_DEVICE_WAIT) or SPAMM_OK. */
 int spamm_sync(spamm_plan *plan);
