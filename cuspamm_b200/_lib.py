@@ -53,6 +53,7 @@ SIGNATURES = {
     "spamm_pack": (_i, [_vp]),
     "spamm_gated_multiply": (_i, [_vp]),
     "spamm_run": (_i, [_vp, _f]),
+    "spamm_finish": (_i, [_vp, _f]),
     "spamm_sync": (_i, [_vp]),
     "spamm_download_c": (_i, [_vp, _vp]),
     "spamm_multiply": (_i, [_vp, _vp, _vp, _vp, _f, C.POINTER(SpammStats)]),
@@ -71,6 +72,7 @@ SIGNATURES = {
     "spamm_stream": (_i, [_vp, _pp]),
     "spamm_plan_dims": (_i, [_vp] + [C.POINTER(_i)] * 5),
     "spamm_norm_map_dev": (_i, [_vp, _i, _i, _i64, _vp, _vp]),
+    "spamm_norm_map_pair_dev": (_i, [_vp, _i, _i, _i64, _vp, _vp, _i, _i, _i64, _vp, _vp]),
     "spamm_build_lists_scratch_bytes": (_sz, [_i, _i, _i]),
     "spamm_build_lists_dev": (_i, [_vp, _vp, _i, _i, _i, _f] + [_vp] * 10),
     "spamm_pack_half_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

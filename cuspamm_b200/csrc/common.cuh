@@ -29,6 +29,21 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int record_cuda_error(cudaError_t e, const char *what);
 void record_error_text(const char *text);
 
+// Internal launchers behind the extern "C" entry points, with the extras the plan uses to save launches:
+//  - the list builder's first kernel can clear a region (counters + need flags) before the lists are built,
+//  - the packing kernel can reset the multiply's two work counters, which the multiply launcher then leaves alone.
+int build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles, float tau,
+                       void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
+                       uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list, int32_t *d_busy_list,
+                       spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes, cudaStream_t stream);
+int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
+                     const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
+                     bool reset_queues, cudaStream_t stream);
+int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
+                          const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
+                          spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
+                          int64_t ldc, bool reset_queues, cudaStream_t stream);
+
 #define SPAMM_CUDA_TRY(call)                                                    \
     do {                                                                        \
         cudaError_t e__ = (call);                                               \

@@ -599,6 +599,15 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
                                         const int32_t *d_busy_list, spamm_list_scalars *d_scalars, int row_tiles,
                                         int k_tiles, int n_tiles, float *d_c, int64_t ldc, void *stream)
 {
+    return spamm::gated_multiply_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_order, d_busy_list, d_scalars,
+                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, (cudaStream_t)stream);
+}
+
+int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
+                                 const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
+                                 spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
+                                 int64_t ldc, bool reset_queues, cudaStream_t stream)
+{
     using namespace spamm;
     if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
         k_tiles < 0 || n_tiles < 0 || ldc < (int64_t)n_tiles * TILE || (ldc & 3) ||
@@ -624,10 +633,10 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
         sm_count_of[dev] = sms;
     }
     const int sm_count = sm_count_of[dev];
-    // the two work counters start from zero at every launch
-    SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 2 * sizeof(unsigned int), (cudaStream_t)stream));
+    // the two work counters start from zero at every launch (unless the packing kernel just reset them)
+    if (reset_queues) SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 2 * sizeof(unsigned int), stream));
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
-    gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, (cudaStream_t)stream>>>(
+    gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, stream>>>(
         static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
         d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc);
     SPAMM_CUDA_TRY(cudaGetLastError());

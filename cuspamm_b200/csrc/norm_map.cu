@@ -15,12 +15,12 @@
 
 namespace spamm {
 
-__global__ void __launch_bounds__(256)
-norm_map_kernel(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld, float *__restrict__ map)
+// One strip of four tiles per warp; `strip` counts strips of this matrix in row-major order.
+__device__ __forceinline__ void norm_strip(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld,
+                                           float *__restrict__ map, int64_t strip)
 {
     const int lane = threadIdx.x & 31;
     const int strips_per_row = (tile_cols + 3) >> 2;
-    const int64_t strip = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (strip >= (int64_t)tile_rows * strips_per_row) return;
     const int tr = (int)(strip / strips_per_row);
     const int ts = (int)(strip % strips_per_row);
@@ -53,6 +53,25 @@ norm_map_kernel(const float *__restrict__ x, int tile_rows, int tile_cols, int64
     }
 }
 
+__global__ void __launch_bounds__(256)
+norm_map_kernel(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld, float *__restrict__ map)
+{
+    norm_strip(x, tile_rows, tile_cols, ld, map, (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5));
+}
+
+// Two matrices in one launch (the A rows and B of one SpAMM step): blocks [0, blocks_a) work on the first.
+__global__ void __launch_bounds__(256)
+norm_map_pair_kernel(const float *__restrict__ xa, int tile_rows_a, int tile_cols_a, int64_t lda,
+                     float *__restrict__ map_a, unsigned int blocks_a, const float *__restrict__ xb, int tile_rows_b,
+                     int tile_cols_b, int64_t ldb, float *__restrict__ map_b)
+{
+    if (blockIdx.x < blocks_a)
+        norm_strip(xa, tile_rows_a, tile_cols_a, lda, map_a, (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5));
+    else
+        norm_strip(xb, tile_rows_b, tile_cols_b, ldb, map_b,
+                   (int64_t)(blockIdx.x - blocks_a) * 8 + (threadIdx.x >> 5));
+}
+
 }  // namespace spamm
 
 extern "C" int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t ld, float *d_map, void *stream)
@@ -67,6 +86,26 @@ extern "C" int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t 
     const int64_t blocks = (strips + 7) / 8;
     if (blocks > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
     norm_map_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(d_x, tile_rows, tile_cols, ld, d_map);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}
+
+extern "C" int spamm_norm_map_pair_dev(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a,
+                                       const float *d_xb, int rows_b, int cols_b, int64_t ldb, float *d_map_b,
+                                       void *stream)
+{
+    using namespace spamm;
+    if (!d_xa || !d_map_a || !d_xb || !d_map_b || rows_a < 0 || cols_a < 0 || rows_b < 0 || cols_b < 0 ||
+        rows_a % TILE || cols_a % TILE || rows_b % TILE || cols_b % TILE || lda < cols_a || ldb < cols_b ||
+        (lda & 3) || (ldb & 3) || (reinterpret_cast<uintptr_t>(d_xa) & 15) || (reinterpret_cast<uintptr_t>(d_xb) & 15))
+        return SPAMM_ERR_INVALID;
+    const int tra = rows_a / TILE, tca = cols_a / TILE, trb = rows_b / TILE, tcb = cols_b / TILE;
+    const int64_t blocks_a = ((int64_t)tra * ((tca + 3) / 4) + 7) / 8;
+    const int64_t blocks_b = ((int64_t)trb * ((tcb + 3) / 4) + 7) / 8;
+    if (blocks_a + blocks_b == 0) return SPAMM_OK;
+    if (blocks_a + blocks_b > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+    norm_map_pair_kernel<<<(unsigned)(blocks_a + blocks_b), 256, 0, (cudaStream_t)stream>>>(
+        d_xa, tra, tca, lda, d_map_a, (unsigned)blocks_a, d_xb, trb, tcb, ldb, d_map_b);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

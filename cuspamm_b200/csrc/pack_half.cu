@@ -32,8 +32,10 @@ __device__ __forceinline__ uint4 pack8(const float *f)
 __global__ void __launch_bounds__(256)
 pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k_tiles, int n_tiles,
                  const uint32_t *__restrict__ tile_list, spamm_list_scalars *__restrict__ sc,
-                 uint8_t *__restrict__ half_a, uint8_t *__restrict__ half_b)
+                 uint8_t *__restrict__ half_a, uint8_t *__restrict__ half_b, int reset_queues)
 {
+    // optional: the multiply kernel (next on the stream) starts its two work counters from zero
+    if (reset_queues && blockIdx.x == 0 && threadIdx.x < 2) (&sc->queue_busy)[threadIdx.x] = 0u;
     __shared__ float tr[8][TILE][TILE + 1];
     __shared__ unsigned int blk_cnt[2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -96,6 +98,14 @@ extern "C" int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_t
                                    const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a,
                                    void *d_half_b, void *stream)
 {
+    return spamm::pack_half_launch(d_a, d_b, row_tiles, k_tiles, n_tiles, d_tile_list, d_scalars, d_half_a, d_half_b,
+                                   false, (cudaStream_t)stream);
+}
+
+int spamm::pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
+                            const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
+                            bool reset_queues, cudaStream_t stream)
+{
     using namespace spamm;
     if (!d_a || !d_b || !d_tile_list || !d_scalars || !d_half_a || !d_half_b || row_tiles < 0 || k_tiles < 0 ||
         n_tiles < 0)
@@ -109,9 +119,9 @@ extern "C" int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_t
     int64_t blocks = (total + 7) / 8;
     const int64_t max_blocks = 148 * 8;
     if (blocks > max_blocks) blocks = max_blocks;
-    pack_half_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+    pack_half_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
         d_a, d_b, k_tiles, n_tiles, d_tile_list, d_scalars, static_cast<uint8_t *>(d_half_a),
-        static_cast<uint8_t *>(d_half_b));
+        static_cast<uint8_t *>(d_half_b), reset_queues ? 1 : 0);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

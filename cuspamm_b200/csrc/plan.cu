@@ -61,7 +61,8 @@ struct spamm_plan {
     int chunk_tiles = 0;                // tile rows per chunk of the pipelined spamm_multiply (multiple of 4)
     int n_chunks = 1;
     int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
-    int active_scalars = 1;             // how many scalar sets the last operation used
+    int active_scalars = 1;
+    bool queues_clean = false;          // the packing kernel has reset the multiply's work counters             // how many scalar sets the last operation used
     bool have_norms = false, have_lists = false, have_pack = false;
     int64_t launches = 0;
 
@@ -337,7 +338,24 @@ int spamm_norms_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
 int spamm_norms(spamm_plan *p)
 {
     if (!p) return SPAMM_ERR_INVALID;
-    return spamm_norms_share(p, 0, p->k_tiles);
+    if (p->row_tiles == 0) return spamm_norms_share(p, 0, p->k_tiles);
+    DeviceGuard guard(p->device);
+    // both maps in one launch
+    int st = spamm_norm_map_pair_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->d_b, p->K, p->N, p->N,
+                                     p->d_norm_b, p->stream);
+    if (st) return st;
+    p->launches++;
+    p->have_norms = true;
+    p->have_lists = p->have_pack = false;
+    return SPAMM_OK;
+}
+
+int spamm_finish(spamm_plan *p, float tau)
+{
+    int st;
+    if ((st = spamm_build_lists(p, tau))) return st;
+    if ((st = spamm_pack(p))) return st;
+    return spamm_gated_multiply(p);
 }
 
 int spamm_build_lists(spamm_plan *p, float tau)
@@ -345,14 +363,17 @@ int spamm_build_lists(spamm_plan *p, float tau)
     if (!p) return SPAMM_ERR_INVALID;
     if (!p->have_norms) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
-    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
     p->active_scalars = 1;
     if (p->row_tiles) {
-        int st = spamm_build_lists_dev(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
-                                       p->d_list_scratch, p->d_steps, p->d_step_counts, p->d_counts, p->need_a(),
-                                       p->need_b(), p->d_tile_list, p->d_busy, p->scalars(), p->stream);
+        // the builder's first kernel clears the counters and need flags: no separate memset on the stream
+        int st = build_lists_launch(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
+                                    p->d_list_scratch, p->d_steps, p->d_step_counts, p->d_counts, p->need_a(),
+                                    p->need_b(), p->d_tile_list, p->d_busy, p->scalars(), p->d_cleared,
+                                    p->cleared_bytes, p->stream);
         if (st) return st;
         p->launches += 2;
+    } else {
+        SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
     }
     p->have_lists = true;
     p->have_pack = false;
@@ -365,10 +386,11 @@ int spamm_pack(spamm_plan *p)
     if (!p->have_lists) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     if (p->row_tiles) {
-        int st = spamm_pack_half_dev(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->d_tile_list,
-                                     p->scalars(), p->d_half_a, p->d_half_b, p->stream);
+        int st = pack_half_launch(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->d_tile_list, p->scalars(),
+                                  p->d_half_a, p->d_half_b, true, p->stream);
         if (st) return st;
         p->launches++;
+        p->queues_clean = true;
     }
     p->have_pack = true;
     return SPAMM_OK;
@@ -380,8 +402,10 @@ int spamm_gated_multiply(spamm_plan *p)
     if (!p->have_pack) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     if (p->row_tiles) {
-        int st = spamm_gated_multiply_dev(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
-                                          p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, p->stream);
+        int st = gated_multiply_launch(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
+                                       p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N,
+                                       !p->queues_clean, p->stream);
+        p->queues_clean = false;
         if (st) return st;
         p->launches++;
     }
@@ -512,12 +536,12 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
                                     p->d_tile_list, p->d_busy + mt0, sc, p->stream)))
         return st;
     uint8_t *half_a = p->d_half_a + mi0 * p->k_tiles * A_SLAB_BYTES;
-    if ((st = spamm_pack_half_dev(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b,
-                                  p->stream)))
+    if ((st = pack_half_launch(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b, true,
+                               p->stream)))
         return st;
-    if ((st = spamm_gated_multiply_dev(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
-                                       d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                       p->d_c + (size_t)t0 * TILE * p->N, p->N, p->stream)))
+    if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
+                                    d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->stream)))
         return st;
     p->launches += 5;
     return SPAMM_OK;

@@ -27,8 +27,12 @@ namespace spamm {
 // tile columns 8mj..8mj+7.  One warp per output value.
 __global__ void __launch_bounds__(256)
 chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
-                 int n_tiles, float *__restrict__ amax, float *__restrict__ bmax)
+                 int n_tiles, float *__restrict__ amax, float *__restrict__ bmax, uint4 *__restrict__ clear,
+                 size_t clear_vecs)
 {
+    // optional: zero the counters and need flags the list builder (the next kernel) starts from
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < clear_vecs; i += (size_t)gridDim.x * blockDim.x)
+        clear[i] = make_uint4(0u, 0u, 0u, 0u);
     const int lane = threadIdx.x & 31;
     const int mi_n = (row_tiles + MT_R - 1) / MT_R;
     const int mj_n = (n_tiles + MT_C - 1) / MT_C;
@@ -256,17 +260,18 @@ extern "C" size_t spamm_build_lists_scratch_bytes(int row_tiles, int k_tiles, in
     return sizeof(float) * kc_n * ((size_t)ceil_div(row_tiles, MT_R) + ceil_div(n_tiles, MT_C)) + 16;
 }
 
-extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles,
-                                     int n_tiles, float tau, void *d_scratch, uint32_t *d_steps,
-                                     int32_t *d_step_counts, int32_t *d_counts, uint8_t *d_need_a, uint8_t *d_need_b,
-                                     uint32_t *d_tile_list, int32_t *d_busy_list, spamm_list_scalars *d_scalars,
-                                     void *stream)
+int spamm::build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,
+                              float tau, void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts,
+                              int32_t *d_counts, uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list,
+                              int32_t *d_busy_list, spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes,
+                              cudaStream_t stream)
 {
     using namespace spamm;
     if (!d_norm_a || !d_norm_b || !d_scratch || !d_steps || !d_step_counts || !d_counts || !d_need_a || !d_need_b ||
         !d_tile_list || !d_busy_list || !d_scalars || row_tiles < 0 || k_tiles < 0 || n_tiles < 0 || k_tiles > 65535)
         return SPAMM_ERR_INVALID;
-    if ((reinterpret_cast<uintptr_t>(d_scratch) & 3) || (reinterpret_cast<uintptr_t>(d_scalars) & 7))
+    if ((reinterpret_cast<uintptr_t>(d_scratch) & 3) || (reinterpret_cast<uintptr_t>(d_scalars) & 7) ||
+        (reinterpret_cast<uintptr_t>(d_clear) & 15) || (clear_bytes & 15))
         return SPAMM_ERR_INVALID;
     const int mi_n = ceil_div(row_tiles, MT_R), mj_n = ceil_div(n_tiles, MT_C), kc_n = ceil_div(k_tiles, 32);
     const int64_t mts = (int64_t)mi_n * mj_n;
@@ -277,12 +282,25 @@ extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_
     float *amax = static_cast<float *>(d_scratch);
     float *bmax = amax + (size_t)mi_n * kc_n;
     const int64_t warps = (int64_t)kc_n * (mi_n + mj_n);
-    if (warps > 0)
-        chunk_max_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(d_norm_a, d_norm_b, row_tiles,
-                                                                                       k_tiles, n_tiles, amax, bmax);
-    build_lists_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(
+    int64_t cm_blocks = (warps + 7) / 8;
+    if (cm_blocks < 1) cm_blocks = 1;
+    chunk_max_kernel<<<(unsigned)cm_blocks, 256, 0, stream>>>(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, amax,
+                                                             bmax, static_cast<uint4 *>(d_clear),
+                                                             d_clear ? clear_bytes / 16 : 0);
+    build_lists_kernel<<<(unsigned)blocks, 128, 0, stream>>>(
         d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, amax, bmax, d_steps, d_step_counts, d_counts, d_need_a,
         d_need_b, d_tile_list, d_busy_list, d_scalars);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
+}
+
+extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles,
+                                     int n_tiles, float tau, void *d_scratch, uint32_t *d_steps,
+                                     int32_t *d_step_counts, int32_t *d_counts, uint8_t *d_need_a, uint8_t *d_need_b,
+                                     uint32_t *d_tile_list, int32_t *d_busy_list, spamm_list_scalars *d_scalars,
+                                     void *stream)
+{
+    return spamm::build_lists_launch(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, d_scratch, d_steps,
+                                     d_step_counts, d_counts, d_need_a, d_need_b, d_tile_list, d_busy_list, d_scalars,
+                                     nullptr, 0, (cudaStream_t)stream);
 }

@@ -150,6 +150,10 @@ class SpammPlan:
     def run(self, tau: float) -> None:
         check(self._lib.spamm_run(self._h, float(tau)), "spamm_run")
 
+    def finish(self, tau: float) -> None:
+        """lists + pack + multiply in one call."""
+        check(self._lib.spamm_finish(self._h, float(tau)), "spamm_finish")
+
     def sync(self) -> None:
         check(self._lib.spamm_sync(self._h), "spamm_sync")
 
@@ -328,9 +332,13 @@ class ShardedSpamm:
                 self.plan.norms_share(self.rank * self._share, self._share)
                 parts = [nb[r * self._share:(r + 1) * self._share] for r in range(self.world)]
                 self._dist.all_gather(parts, mine.clone(), group=self.group)
-        self.plan.build_lists(tau)
-        self.plan.pack()
-        self.plan.gated_multiply()
+        finish = getattr(self.plan, "finish", None)
+        if finish is not None:
+            finish(tau)
+        else:
+            self.plan.build_lists(tau)
+            self.plan.pack()
+            self.plan.gated_multiply()
 
     def run_timed(self, tau: float) -> dict:
         """One `run` with CUDA events between its parts (this rank's view, milliseconds); blocking."""

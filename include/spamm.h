@@ -126,6 +126,8 @@ int spamm_build_lists(spamm_plan *plan, float tau);
 int spamm_pack(spamm_plan *plan);
 int spamm_gated_multiply(spamm_plan *plan);
 int spamm_run(spamm_plan *plan, float tau);
+/* spamm_build_lists + spamm_pack + spamm_gated_multiply in one call (what follows the norm maps). */
+int spamm_finish(spamm_plan *plan, float tau);
 
 /*
  * spamm_norms with only tile rows [b_tile_begin, b_tile_begin+b_tile_count) of B's norm map computed here; the
@@ -206,6 +208,9 @@ int spamm_plan_dims(spamm_plan *plan, int *M, int *K, int *N, int *row_tile_begi
  * d_x must be 16-byte aligned and ld a multiple of 4.
  */
 int spamm_norm_map_dev(const float *d_x, int rows, int cols, int64_t ld, float *d_map, void *stream);
+/* The same for two matrices in one launch (the A rows and B of one step). */
+int spamm_norm_map_pair_dev(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a,
+                            const float *d_xb, int rows_b, int cols_b, int64_t ldb, float *d_map_b, void *stream);
 
 /*
  * Skip-list build (cuSpAMM.cu:302-334) for row_tiles x (N/32) C tiles.  For every macro tile of
