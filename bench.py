@@ -309,6 +309,18 @@ def run_ours(args):
         sh.run(tau)
         sh.sync()
 
+    # ---- multi-GPU: the dense limit (tau = 0) beside the headline, where a step is milliseconds of tensor work
+    dense_multi = None
+    if world > 1 and not args.no_sweep:
+        for _ in range(2):
+            sh.run(0.0)
+        sh.sync()
+        ms_d = timed(lambda: sh.run(0.0), 3)
+        s_d = sh.survivors()
+        dense_multi = {"tau": 0.0, "ms": ms_d, "survivors": s_d, "executed_tflops": 65536.0 * s_d / (ms_d * 1e-3) / 1e12}
+        sh.run(tau)
+        sh.sync()
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -331,6 +343,8 @@ def run_ours(args):
     }
     if phase is not None and world > 1:
         line["phases_ms_rank0"] = phase
+    if dense_multi is not None:
+        line["dense_tau0"] = dense_multi
     if phase is not None and world == 1:
         norm_bytes = 8.0 * n * n   # every float of A and of B read once
         achieved = norm_bytes / (phase["ms_norm"] * 1e-3) / 1e9
