@@ -196,7 +196,7 @@ def run_ours(args):
     n, tau = args.n, args.tau
     peaks = read_peaks()
 
-    sh = ShardedSpamm(n, n, n)
+    sh = ShardedSpamm(n, n, n, exchange=args.exchange)
     plan = sh.plan
     rows = plan.rows
     a_t, a_np = pinned((rows, n))
@@ -266,10 +266,15 @@ def run_ours(args):
     elif sh._share is not None:
         acc = {}
         reps = max(3, min(args.steps, 10))
+        exch = None
         for _ in range(reps):
             for k, v in sh.run_timed(tau).items():
-                acc[k] = acc.get(k, 0.0) + v
+                if isinstance(v, str):
+                    exch = v
+                else:
+                    acc[k] = acc.get(k, 0.0) + v
         phase = {k: v / reps for k, v in acc.items()}      # rank 0's view
+        phase["exchange"] = exch
 
     # ---- end to end through the public call with host buffers (pinned): H2D + device + gather + D2H
     e2e_steps = max(1, min(args.steps, 3))
@@ -403,6 +408,8 @@ def main():
     ap.add_argument("--tau", type=float, default=1e-6)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--exchange", default="nccl", choices=["push", "nccl"],
+                    help="multi-GPU: how B's norm-map shares travel (peer stores from the norm kernel, or NCCL all-gather)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -49,6 +49,9 @@ SIGNATURES = {
     "spamm_norms_share": (_i, [_vp, _i, _i]),
     "spamm_norm_b_share": (_i, [_vp, _i, _i]),
     "spamm_norm_a": (_i, [_vp]),
+    "spamm_peer_handles": (_i, [_vp, _vp, _sz]),
+    "spamm_peer_attach": (_i, [_vp, _i, _i, _vp]),
+    "spamm_norm_b_share_push": (_i, [_vp, _i, _i]),
     "spamm_build_lists": (_i, [_vp, _f]),
     "spamm_pack": (_i, [_vp]),
     "spamm_gated_multiply": (_i, [_vp]),

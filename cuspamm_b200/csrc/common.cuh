@@ -29,13 +29,30 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int record_cuda_error(cudaError_t e, const char *what);
 void record_error_text(const char *text);
 
+// Peer-to-peer exchange of B's norm-map shares between the GPUs of one box (one process per GPU).
+constexpr int MAX_PEERS = 8;
+struct PeerTargets {
+    float *map[MAX_PEERS];            // the norm map of B of every GPU (this one included), peer-mapped
+    unsigned int *flags[MAX_PEERS];   // every GPU's arrival flags, one word per sender
+    int n;
+};
+struct PeerWait {                     // what the list builder waits for before it reads B's map
+    const unsigned int *flags;        // this GPU's arrival flags
+    int n;                            // senders
+    unsigned int epoch;               // value every flag must have reached
+    int *error;                       // set when the wait runs out
+};
+int norm_map_push_launch(const float *d_x, int rows, int cols, int64_t ld, int64_t map_offset, const PeerTargets &t,
+                         int rank, unsigned int epoch, cudaStream_t stream);
+
 // Internal launchers behind the extern "C" entry points, with the extras the plan uses to save launches:
 //  - the list builder's first kernel can clear a region (counters + need flags) before the lists are built,
 //  - the packing kernel can reset the multiply's two work counters, which the multiply launcher then leaves alone.
 int build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles, float tau,
                        void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
                        uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list, int32_t *d_busy_list,
-                       spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes, cudaStream_t stream);
+                       spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes, const PeerWait *wait,
+                       cudaStream_t stream);
 int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
                      const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
                      bool reset_queues, cudaStream_t stream);

@@ -15,13 +15,14 @@
 
 namespace spamm {
 
-// One strip of four tiles per warp; `strip` counts strips of this matrix in row-major order.
-__device__ __forceinline__ void norm_strip(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld,
-                                           float *__restrict__ map, int64_t strip)
+// One strip of four tiles per warp; `strip` counts strips of this matrix in row-major order.  Returns true in the
+// lanes that hold a finished tile norm (*value) and its index in the map (*index).
+__device__ __forceinline__ bool norm_strip_value(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld,
+                                                 int64_t strip, float *value, int64_t *index)
 {
     const int lane = threadIdx.x & 31;
     const int strips_per_row = (tile_cols + 3) >> 2;
-    if (strip >= (int64_t)tile_rows * strips_per_row) return;
+    if (strip >= (int64_t)tile_rows * strips_per_row) return false;
     const int tr = (int)(strip / strips_per_row);
     const int ts = (int)(strip % strips_per_row);
     const int col = ts * 128 + lane * 4;
@@ -48,9 +49,17 @@ __device__ __forceinline__ void norm_strip(const float *__restrict__ x, int tile
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-    if (in_range && (lane & 7) == 0) {
-        map[(int64_t)tr * tile_cols + ts * 4 + (lane >> 3)] = __fsqrt_rn(acc);
-    }
+    *value = __fsqrt_rn(acc);
+    *index = (int64_t)tr * tile_cols + ts * 4 + (lane >> 3);
+    return in_range && (lane & 7) == 0;
+}
+
+__device__ __forceinline__ void norm_strip(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld,
+                                           float *__restrict__ map, int64_t strip)
+{
+    float v;
+    int64_t i;
+    if (norm_strip_value(x, tile_rows, tile_cols, ld, strip, &v, &i)) map[i] = v;
 }
 
 __global__ void __launch_bounds__(256)
@@ -70,6 +79,44 @@ norm_map_pair_kernel(const float *__restrict__ xa, int tile_rows_a, int tile_col
     else
         norm_strip(xb, tile_rows_b, tile_cols_b, ldb, map_b,
                    (int64_t)(blockIdx.x - blocks_a) * 8 + (threadIdx.x >> 5));
+}
+
+// All-gather of B's norm-map shares without a collective call: after the norm kernel has written this GPU's share
+// into its own map, one block per destination GPU copies the share into that GPU's map (peer-mapped memory, plain
+// 128-bit stores over NVLink), fences system-wide and raises this GPU's flag there: "share of `rank` for step
+// `epoch` has arrived".  The reader (the list builder's first kernel) waits for all flags with a time limit.
+__global__ void __launch_bounds__(256)
+push_share_kernel(const float4 *__restrict__ src, int64_t vecs, int64_t map_offset_vecs, PeerTargets t, int self,
+                  unsigned int epoch)
+{
+    const int d = blockIdx.x;                       // destination GPU
+    if (d != self) {
+        float4 *dst = reinterpret_cast<float4 *>(t.map[d]) + map_offset_vecs;
+        for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();                                // orders the block's stores before the fence below
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(t.flags[d] + self), "r"(epoch) : "memory");
+    }
+}
+
+int norm_map_push_launch(const float *d_x, int rows, int cols, int64_t ld, int64_t map_offset, const PeerTargets &t,
+                         int rank, unsigned int epoch, cudaStream_t stream)
+{
+    if (!d_x || rows <= 0 || cols <= 0 || rows % TILE || cols % TILE || (ld & 3) || t.n <= 0 || t.n > MAX_PEERS ||
+        rank < 0 || rank >= t.n)
+        return SPAMM_ERR_INVALID;
+    const int tile_rows = rows / TILE, tile_cols = cols / TILE;
+    const int64_t share = (int64_t)tile_rows * tile_cols;          // floats in this GPU's share of the map
+    float *local = t.map[rank] + map_offset;
+    if ((share & 3) || (map_offset & 3) || (reinterpret_cast<uintptr_t>(local) & 15)) return SPAMM_ERR_UNSUPPORTED;
+    int st = spamm_norm_map_dev(d_x, rows, cols, ld, local, stream);
+    if (st) return st;
+    push_share_kernel<<<t.n, 256, 0, stream>>>(reinterpret_cast<const float4 *>(local), share / 4, map_offset / 4, t,
+                                              rank, epoch);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
 }
 
 }  // namespace spamm

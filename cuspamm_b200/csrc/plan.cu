@@ -62,7 +62,18 @@ struct spamm_plan {
     int n_chunks = 1;
     int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
     int active_scalars = 1;
-    bool queues_clean = false;          // the packing kernel has reset the multiply's work counters             // how many scalar sets the last operation used
+    bool queues_clean = false;
+    // peer exchange of B's norm-map shares (one process per GPU, see spamm_peer_attach)
+    float *d_norm_b_buf[2] = {nullptr, nullptr};   // B's map, double buffered by step parity; d_norm_b is the current
+    unsigned int *d_peer_flags = nullptr;          // [MAX_PEERS] arrival flags + [1] block counter of the push kernel
+    int *d_peer_error = nullptr;
+    int *h_peer_error = nullptr;                   // pinned
+    int peer_world = 0, peer_rank = 0;
+    unsigned int peer_epoch = 0;
+    bool peer_wait_pending = false;
+    void *peer_mapped[MAX_PEERS][3] = {};          // what cudaIpcOpenMemHandle returned, per peer
+    float *peer_norm_b[MAX_PEERS][2] = {};
+    unsigned int *peer_flags[MAX_PEERS] = {};          // the packing kernel has reset the multiply's work counters             // how many scalar sets the last operation used
     bool have_norms = false, have_lists = false, have_pack = false;
     int64_t launches = 0;
 
@@ -118,12 +129,16 @@ int read_scalars(spamm_plan *p)
 {
     SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_scalars, p->scalars(), sizeof(DeviceScalars) * p->active_scalars,
                                    cudaMemcpyDeviceToHost, p->stream));
+    if (p->peer_world > 1)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_peer_error, p->d_peer_error, sizeof(int), cudaMemcpyDeviceToHost,
+                                       p->stream));
     SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
     return SPAMM_OK;
 }
 
 int status_from_scalars(const spamm_plan *p)
 {
+    if (p->peer_world > 1 && *p->h_peer_error) return SPAMM_ERR_DEVICE_WAIT;
     for (int c = 0; c < p->active_scalars; c++) {
         if (p->h_scalars[c].error) return SPAMM_ERR_DEVICE_WAIT;
         if (p->h_scalars[c].overflow) return SPAMM_ERR_OVERFLOW;
@@ -225,7 +240,16 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     if ((st = dev_alloc(&p->d_b, p->bytes_b()))) return fail(st);
     if ((st = dev_alloc(&p->d_c, p->bytes_c()))) return fail(st);
     if ((st = dev_alloc(&p->d_norm_a, p->bytes_norm_a()))) return fail(st);
-    if ((st = dev_alloc(&p->d_norm_b, p->bytes_norm_b()))) return fail(st);
+    if ((st = dev_alloc(&p->d_norm_b_buf[0], p->bytes_norm_b()))) return fail(st);
+    if ((st = dev_alloc(&p->d_norm_b_buf[1], p->bytes_norm_b()))) return fail(st);
+    p->d_norm_b = p->d_norm_b_buf[0];
+    if ((st = dev_alloc(&p->d_peer_flags, sizeof(unsigned int) * (MAX_PEERS + 8)))) return fail(st);
+    if ((st = dev_alloc(&p->d_peer_error, sizeof(int)))) return fail(st);
+    if (cudaMemset(p->d_peer_flags, 0, sizeof(unsigned int) * (MAX_PEERS + 8)) != cudaSuccess ||
+        cudaMemset(p->d_peer_error, 0, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void **>(&p->h_peer_error), sizeof(int)) != cudaSuccess)
+        return fail(record_cuda_error(cudaGetLastError(), "peer exchange buffers"));
+    *p->h_peer_error = 0;
     if ((st = dev_alloc(&p->d_counts, p->bytes_counts()))) return fail(st);
     if ((st = dev_alloc(&p->d_step_counts, p->bytes_step_counts()))) return fail(st);
     if ((st = dev_alloc(&p->d_steps, p->bytes_steps()))) return fail(st);
@@ -270,7 +294,12 @@ int spamm_plan_destroy(spamm_plan *p)
     DeviceGuard guard(p->device);
     if (p->stream) cudaStreamSynchronize(p->stream);
     cudaFree(p->d_a); cudaFree(p->d_b); cudaFree(p->d_c);
-    cudaFree(p->d_norm_a); cudaFree(p->d_norm_b);
+    for (int r = 0; r < MAX_PEERS; r++)
+        for (int i = 0; i < 3; i++)
+            if (p->peer_mapped[r][i]) cudaIpcCloseMemHandle(p->peer_mapped[r][i]);
+    cudaFree(p->d_norm_a); cudaFree(p->d_norm_b_buf[0]); cudaFree(p->d_norm_b_buf[1]);
+    cudaFree(p->d_peer_flags); cudaFree(p->d_peer_error);
+    if (p->h_peer_error) cudaFreeHost(p->h_peer_error);
     cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
     cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared); cudaFree(p->d_order);
     cudaFree(p->d_busy); cudaFree(p->d_tile_list); cudaFree(p->d_list_scratch);
@@ -335,6 +364,69 @@ int spamm_norms_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
     return spamm_norm_a(p);
 }
 
+int spamm_peer_handles(spamm_plan *p, void *out, size_t out_bytes)
+{
+    if (!p || !out || out_bytes < 3 * sizeof(cudaIpcMemHandle_t)) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    cudaIpcMemHandle_t *h = static_cast<cudaIpcMemHandle_t *>(out);
+    SPAMM_CUDA_TRY(cudaIpcGetMemHandle(&h[0], p->d_norm_b_buf[0]));
+    SPAMM_CUDA_TRY(cudaIpcGetMemHandle(&h[1], p->d_norm_b_buf[1]));
+    SPAMM_CUDA_TRY(cudaIpcGetMemHandle(&h[2], p->d_peer_flags));
+    return SPAMM_OK;
+}
+
+int spamm_peer_attach(spamm_plan *p, int world, int rank, const void *all_handles)
+{
+    if (!p || !all_handles || world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) return SPAMM_ERR_INVALID;
+    if (p->peer_world) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(all_handles);
+    for (int r = 0; r < world; r++) {
+        if (r == rank) {
+            p->peer_norm_b[r][0] = p->d_norm_b_buf[0];
+            p->peer_norm_b[r][1] = p->d_norm_b_buf[1];
+            p->peer_flags[r] = p->d_peer_flags;
+            continue;
+        }
+        for (int i = 0; i < 3; i++) {
+            cudaError_t e = cudaIpcOpenMemHandle(&p->peer_mapped[r][i], h[r * 3 + i], cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) return record_cuda_error(e, "cudaIpcOpenMemHandle");
+        }
+        p->peer_norm_b[r][0] = static_cast<float *>(p->peer_mapped[r][0]);
+        p->peer_norm_b[r][1] = static_cast<float *>(p->peer_mapped[r][1]);
+        p->peer_flags[r] = static_cast<unsigned int *>(p->peer_mapped[r][2]);
+    }
+    p->peer_world = world;
+    p->peer_rank = rank;
+    return SPAMM_OK;
+}
+
+int spamm_norm_b_share_push(spamm_plan *p, int b_tile_begin, int b_tile_count)
+{
+    if (!p || b_tile_begin < 0 || b_tile_count <= 0 || b_tile_begin + (int64_t)b_tile_count > p->k_tiles)
+        return SPAMM_ERR_INVALID;
+    if (p->peer_world < 2) return SPAMM_ERR_STATE;
+    DeviceGuard guard(p->device);
+    // A new step: its shares go to the other buffer of every GPU, so a GPU that is still building the previous
+    // step's lists is not disturbed; nobody can be two steps ahead, because every step waits for all flags.
+    p->peer_epoch++;
+    const int buf = (int)(p->peer_epoch & 1u);
+    p->d_norm_b = p->d_norm_b_buf[buf];
+    PeerTargets t{};
+    t.n = p->peer_world;
+    for (int r = 0; r < p->peer_world; r++) {
+        t.map[r] = p->peer_norm_b[r][buf];
+        t.flags[r] = p->peer_flags[r];
+    }
+    int st = norm_map_push_launch(p->d_b + (size_t)b_tile_begin * TILE * p->N, b_tile_count * TILE, p->N, p->N,
+                                  (int64_t)b_tile_begin * p->n_tiles, t, p->peer_rank, p->peer_epoch, p->stream);
+    if (st) return st;
+    p->launches += 2;
+    p->peer_wait_pending = true;
+    p->have_lists = p->have_pack = false;
+    return SPAMM_OK;
+}
+
 int spamm_norms(spamm_plan *p)
 {
     if (!p) return SPAMM_ERR_INVALID;
@@ -364,12 +456,14 @@ int spamm_build_lists(spamm_plan *p, float tau)
     if (!p->have_norms) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     p->active_scalars = 1;
+    PeerWait wait{p->d_peer_flags, p->peer_world, p->peer_epoch, p->d_peer_error};
     if (p->row_tiles) {
         // the builder's first kernel clears the counters and need flags: no separate memset on the stream
         int st = build_lists_launch(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
                                     p->d_list_scratch, p->d_steps, p->d_step_counts, p->d_counts, p->need_a(),
                                     p->need_b(), p->d_tile_list, p->d_busy, p->scalars(), p->d_cleared,
-                                    p->cleared_bytes, p->stream);
+                                    p->cleared_bytes, p->peer_wait_pending ? &wait : nullptr, p->stream);
+        p->peer_wait_pending = false;
         if (st) return st;
         p->launches += 2;
     } else {

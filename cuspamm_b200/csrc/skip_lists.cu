@@ -28,8 +28,28 @@ namespace spamm {
 __global__ void __launch_bounds__(256)
 chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
                  int n_tiles, float *__restrict__ amax, float *__restrict__ bmax, uint4 *__restrict__ clear,
-                 size_t clear_vecs)
+                 size_t clear_vecs, PeerWait wait)
 {
+    // optional: B's norm map is assembled by the other GPUs writing their shares into it; wait (at most 2 s) until
+    // every sender's flag has reached this step's number
+    if (wait.flags) {
+        if ((int)threadIdx.x < wait.n) {
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+                unsigned int f;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(wait.flags + threadIdx.x) : "memory");
+                if ((int)(f - wait.epoch) >= 0) break;
+                unsigned long long t1;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > 2000000000ull) {
+                    atomicExch(wait.error, 1);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
     // optional: zero the counters and need flags the list builder (the next kernel) starts from
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < clear_vecs; i += (size_t)gridDim.x * blockDim.x)
         clear[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -264,7 +284,7 @@ int spamm::build_lists_launch(const float *d_norm_a, const float *d_norm_b, int 
                               float tau, void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts,
                               int32_t *d_counts, uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list,
                               int32_t *d_busy_list, spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes,
-                              cudaStream_t stream)
+                              const PeerWait *wait, cudaStream_t stream)
 {
     using namespace spamm;
     if (!d_norm_a || !d_norm_b || !d_scratch || !d_steps || !d_step_counts || !d_counts || !d_need_a || !d_need_b ||
@@ -284,9 +304,11 @@ int spamm::build_lists_launch(const float *d_norm_a, const float *d_norm_b, int 
     const int64_t warps = (int64_t)kc_n * (mi_n + mj_n);
     int64_t cm_blocks = (warps + 7) / 8;
     if (cm_blocks < 1) cm_blocks = 1;
+    PeerWait w{};
+    if (wait) w = *wait;
     chunk_max_kernel<<<(unsigned)cm_blocks, 256, 0, stream>>>(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, amax,
                                                              bmax, static_cast<uint4 *>(d_clear),
-                                                             d_clear ? clear_bytes / 16 : 0);
+                                                             d_clear ? clear_bytes / 16 : 0, w);
     build_lists_kernel<<<(unsigned)blocks, 128, 0, stream>>>(
         d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, amax, bmax, d_steps, d_step_counts, d_counts, d_need_a,
         d_need_b, d_tile_list, d_busy_list, d_scalars);
@@ -302,5 +324,5 @@ extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_
 {
     return spamm::build_lists_launch(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, d_scratch, d_steps,
                                      d_step_counts, d_counts, d_need_a, d_need_b, d_tile_list, d_busy_list, d_scalars,
-                                     nullptr, 0, (cudaStream_t)stream);
+                                     nullptr, 0, nullptr, (cudaStream_t)stream);
 }

@@ -135,6 +135,17 @@ class SpammPlan:
     def norm_b_share(self, b_tile_begin: int, b_tile_count: int) -> None:
         check(self._lib.spamm_norm_b_share(self._h, b_tile_begin, b_tile_count), "spamm_norm_b_share")
 
+    def peer_handles(self) -> bytes:
+        buf = C.create_string_buffer(192)
+        check(self._lib.spamm_peer_handles(self._h, buf, 192), "spamm_peer_handles")
+        return buf.raw
+
+    def peer_attach(self, world: int, rank: int, all_handles: bytes) -> None:
+        check(self._lib.spamm_peer_attach(self._h, world, rank, all_handles), "spamm_peer_attach")
+
+    def norm_b_share_push(self, b_tile_begin: int, b_tile_count: int) -> None:
+        check(self._lib.spamm_norm_b_share_push(self._h, b_tile_begin, b_tile_count), "spamm_norm_b_share_push")
+
     def compute_norm_a(self) -> None:
         check(self._lib.spamm_norm_a(self._h), "spamm_norm_a")
 
@@ -271,7 +282,8 @@ class ShardedSpamm:
     device); the tests pass a CPU stand-in to run the same orchestration over gloo.
     """
 
-    def __init__(self, M: int, K: int, N: int, group=None, plan_factory=None, device: Optional[int] = None):
+    def __init__(self, M: int, K: int, N: int, group=None, plan_factory=None, device: Optional[int] = None,
+                 exchange: str = "nccl"):
         import torch
         import torch.distributed as dist
 
@@ -291,6 +303,16 @@ class ShardedSpamm:
         self._share = (k_tiles // self.world) if (self.world > 1 and k_tiles % self.world == 0) else None
         self._nb = self._mine = self._stream = self._side = None
         self._nccl = False
+        # peer-to-peer exchange of B's norm-map shares (no collective in the step) when the plan offers it
+        self._push = False
+        if (exchange == "push" and self._share is not None and (self._share * (N // TILE)) % 4 == 0
+                and hasattr(self.plan, "peer_handles")
+                and self.world <= 8 and dist.get_backend(group) == "nccl"):
+            mine = self.plan.peer_handles()
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=group)
+            self.plan.peer_attach(self.world, self.rank, b"".join(everyone))
+            self._push = True
 
     def _on_stream(self):
         ts = getattr(self.plan, "torch_stream", None)
@@ -311,6 +333,10 @@ class ShardedSpamm:
         """norm maps (B's shared between the ranks), lists, pack, multiply; asynchronous."""
         if self._share is None:
             self.plan.norms()
+        elif self._push:
+            # this rank's share of B's map goes straight into every GPU's map from inside the norm kernel
+            self.plan.norm_b_share_push(self.rank * self._share, self._share)
+            self.plan.compute_norm_a()
         else:
             if self._nb is None:      # views and streams are built once: this runs every step
                 self._nb = self.plan.as_tensor(BUF_NORM_B)
@@ -349,6 +375,10 @@ class ShardedSpamm:
         if self._share is None:
             self.plan.norms()
             ev[1].record(stream)
+        elif self._push:
+            self.plan.norm_b_share_push(self.rank * self._share, self._share)
+            self.plan.compute_norm_a()
+            ev[1].record(stream)       # the wait for the other GPUs' shares is inside the list build
         else:
             self.plan.norms_share(self.rank * self._share, self._share)
             ev[1].record(stream)
@@ -367,6 +397,7 @@ class ShardedSpamm:
         names = ["ms_norm", "ms_allgather", "ms_lists", "ms_pack", "ms_multiply"]
         out = {n: ev[i].elapsed_time(ev[i + 1]) for i, n in enumerate(names)}
         out["ms_device_total"] = ev[0].elapsed_time(ev[5])
+        out["exchange"] = "peer push" if self._push else ("nccl all-gather" if self._share is not None else "none")
         return out
 
     def sync(self) -> None:

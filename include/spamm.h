@@ -139,6 +139,21 @@ int spamm_norms_share(spamm_plan *plan, int b_tile_begin, int b_tile_count);
 int spamm_norm_b_share(spamm_plan *plan, int b_tile_begin, int b_tile_count);
 int spamm_norm_a(spamm_plan *plan);
 
+/*
+ * Exchange of B's norm-map shares without a collective call, for one process per GPU on one box.  Every process
+ * exports three IPC handles of its plan (spamm_peer_handles: 3 x 64 bytes), gathers everybody's (any host-side
+ * all-gather), and attaches them in rank order (spamm_peer_attach: world x 192 bytes, world <= 8).  From then on
+ * spamm_norm_b_share_push computes this GPU's share of B's map and a second small kernel copies it into the map of
+ * EVERY other GPU (plain 128-bit peer stores over NVLink), then raises a flag on every GPU; the next
+ * spamm_build_lists waits, at most 2 s, until all shares of that step have arrived (SPAMM_ERR_DEVICE_WAIT from
+ * spamm_sync otherwise).  B's map is double buffered by step, so a GPU may run one step ahead of the slowest.
+ * Every process must make the same sequence of calls.  The reference recomputes all of B's map on every device
+ * (cuSpAMM.cu:486).
+ */
+int spamm_peer_handles(spamm_plan *plan, void *out, size_t out_bytes);
+int spamm_peer_attach(spamm_plan *plan, int world, int rank, const void *all_handles);
+int spamm_norm_b_share_push(spamm_plan *plan, int b_tile_begin, int b_tile_count);
+
 /* Waits for the plan's stream, then reports a device-side wait that ran out (SPAMM_ERR_DEVICE_WAIT) or SPAMM_OK. */
 int spamm_sync(spamm_plan *plan);
 

@@ -18,15 +18,16 @@ def main():
     from cuspamm_b200 import ShardedSpamm, gen_uniform_alg
 
     n, tau = int(sys.argv[1]), float(sys.argv[2])
+    exchange = sys.argv[3] if len(sys.argv) > 3 else "nccl"
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank = dist.get_rank()
-    sh = ShardedSpamm(n, n, n)
+    sh = ShardedSpamm(n, n, n, exchange=exchange)
     b0, cnt = sh.row_tile_begin, sh.row_tile_count
     A_rows = gen_uniform_alg(3, cnt * 32, n, row_begin=b0 * 32)     # BASELINE config 3 family
     B = gen_uniform_alg(4, n, n) if rank == 0 else None
-    for _ in range(2):                                              # twice: buffers are reused between calls
+    for _ in range(3):                                              # several steps: buffers and flags are reused
         sh.distribute(A_rows, B)
         sh.run(tau)
         S = sh.survivors()
@@ -39,7 +40,7 @@ def main():
         C_ref, S_ref = O.spamm(A, B, tau)
         err = rel_fro(full.cpu().numpy(), C_ref)
         ok = (S == S_ref) and err <= 1e-3
-        print(f"sharded world={dist.get_world_size()} n={n} S={S} S_ref={S_ref} rel_fro={err:.3e} ok={ok}", flush=True)
+        print(f"exchange={exchange} push={sh._push} sharded world={dist.get_world_size()} n={n} S={S} S_ref={S_ref} rel_fro={err:.3e} ok={ok}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
