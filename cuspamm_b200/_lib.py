@@ -52,6 +52,7 @@ SIGNATURES = {
     "spamm_peer_handles": (_i, [_vp, _vp, _sz]),
     "spamm_peer_attach": (_i, [_vp, _i, _i, _vp]),
     "spamm_norm_b_share_push": (_i, [_vp, _i, _i]),
+    "spamm_peer_wait_selftest": (_i, [_vp, _i, C.c_uint]),
     "spamm_build_lists": (_i, [_vp, _f]),
     "spamm_pack": (_i, [_vp]),
     "spamm_gated_multiply": (_i, [_vp]),

@@ -41,7 +41,10 @@ struct PeerWait {                     // what the list builder waits for before 
     int n;                            // senders
     unsigned int epoch;               // value every flag must have reached
     int *error;                       // set when the wait runs out
+    unsigned long long limit_ns;      // how long to wait
 };
+constexpr unsigned long long PEER_WAIT_LIMIT_NS = 2000000000ull;
+int peer_wait_selftest_launch(const PeerWait &w, cudaStream_t stream);
 int norm_map_push_launch(const float *d_x, int rows, int cols, int64_t ld, int64_t map_offset, const PeerTargets &t,
                          int rank, unsigned int epoch, cudaStream_t stream);
 

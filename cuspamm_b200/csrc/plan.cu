@@ -61,6 +61,7 @@ struct spamm_plan {
     int chunk_tiles = 0;                // tile rows per chunk of the pipelined spamm_multiply (multiple of 4)
     int n_chunks = 1;
     int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
+
     int active_scalars = 1;
     bool queues_clean = false;
     // peer exchange of B's norm-map shares (one process per GPU, see spamm_peer_attach)
@@ -401,6 +402,22 @@ int spamm_peer_attach(spamm_plan *p, int world, int rank, const void *all_handle
     return SPAMM_OK;
 }
 
+int spamm_peer_wait_selftest(spamm_plan *p, int senders, unsigned int limit_ms)
+{
+    if (!p || senders < 1 || senders > MAX_PEERS || limit_ms == 0 || limit_ms > 5000) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    // wait for a step number no sender has announced: the wait must run out after limit_ms and say so
+    PeerWait w{p->d_peer_flags, senders, p->peer_epoch + 0x40000000u, p->d_peer_error, (unsigned long long)limit_ms * 1000000ull};
+    int st = peer_wait_selftest_launch(w, p->stream);
+    if (st) return st;
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_peer_error, p->d_peer_error, sizeof(int), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_peer_error, 0, sizeof(int), p->stream));      // leave the plan usable
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    const int expired = *p->h_peer_error;
+    *p->h_peer_error = 0;
+    return expired ? SPAMM_ERR_DEVICE_WAIT : SPAMM_OK;
+}
+
 int spamm_norm_b_share_push(spamm_plan *p, int b_tile_begin, int b_tile_count)
 {
     if (!p || b_tile_begin < 0 || b_tile_count <= 0 || b_tile_begin + (int64_t)b_tile_count > p->k_tiles)
@@ -456,7 +473,7 @@ int spamm_build_lists(spamm_plan *p, float tau)
     if (!p->have_norms) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     p->active_scalars = 1;
-    PeerWait wait{p->d_peer_flags, p->peer_world, p->peer_epoch, p->d_peer_error};
+    PeerWait wait{p->d_peer_flags, p->peer_world, p->peer_epoch, p->d_peer_error, PEER_WAIT_LIMIT_NS};
     if (p->row_tiles) {
         // the builder's first kernel clears the counters and need flags: no separate memset on the stream
         int st = build_lists_launch(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
@@ -608,7 +625,8 @@ int spamm_run_timed(spamm_plan *p, float tau, spamm_stats *stats)
 
 // One chunk of tile rows [t0, t0+tiles) of the plan's block through norm -> lists -> pack -> multiply, with its own
 // set of counters.  Everything the chunk writes lands where the whole-block path would have put it.
-static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, const int32_t *d_order)
+static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, const int32_t *d_order,
+                     cudaStream_t stream, bool do_norm)
 {
     const size_t mi0 = (size_t)t0 / MT_R;                 // chunks start on macro-tile rows
     const size_t mt0 = mi0 * p->mj_n;
@@ -616,28 +634,28 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
     float *a = p->d_a + (size_t)t0 * TILE * p->K;
     float *norm_a = p->d_norm_a + (size_t)t0 * p->k_tiles;
     int st;
-    if ((st = spamm_norm_map_dev(a, tiles * TILE, p->K, p->K, norm_a, p->stream))) return st;
+    if (do_norm && (st = spamm_norm_map_dev(a, tiles * TILE, p->K, p->K, norm_a, stream))) return st;
     if (chunk > 0) {
         // the tile list is shared: this chunk's entries follow the previous chunk's
         SPAMM_CUDA_TRY(cudaMemcpyAsync(&sc->tile_count, &(sc - 1)->tile_count, sizeof(unsigned int),
-                                       cudaMemcpyDeviceToDevice, p->stream));
+                                       cudaMemcpyDeviceToDevice, stream));
         SPAMM_CUDA_TRY(cudaMemcpyAsync(&sc->tile_begin, &(sc - 1)->tile_count, sizeof(unsigned int),
-                                       cudaMemcpyDeviceToDevice, p->stream));
+                                       cudaMemcpyDeviceToDevice, stream));
     }
     if ((st = spamm_build_lists_dev(norm_a, p->d_norm_b, tiles, p->k_tiles, p->n_tiles, tau, p->d_list_scratch,
                                     p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     p->d_counts + (size_t)t0 * p->n_tiles, p->need_a() + mi0 * p->k_tiles, p->need_b(),
-                                    p->d_tile_list, p->d_busy + mt0, sc, p->stream)))
+                                    p->d_tile_list, p->d_busy + mt0, sc, stream)))
         return st;
     uint8_t *half_a = p->d_half_a + mi0 * p->k_tiles * A_SLAB_BYTES;
     if ((st = pack_half_launch(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b, true,
-                               p->stream)))
+                               stream)))
         return st;
     if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->stream)))
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, stream)))
         return st;
-    p->launches += 5;
+    p->launches += do_norm ? 5 : 4;
     return SPAMM_OK;
 }
 
@@ -683,7 +701,8 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
         const size_t a_off = (size_t)t0 * TILE * p->K, c_off = (size_t)t0 * TILE * p->N;
         SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a + a_off, a_rows + a_off, sizeof(float) * (size_t)tiles * TILE * p->K,
                                        cudaMemcpyHostToDevice, p->stream));
-        if ((st = run_chunk(p, c, t0, tiles, tau, c == p->n_chunks - 1 ? p->d_order_last : p->d_order_chunk)))
+        if ((st = run_chunk(p, c, t0, tiles, tau, c == p->n_chunks - 1 ? p->d_order_last : p->d_order_chunk,
+                            p->stream, true)))
             return st;
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev_chunk[c], p->stream));
         SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_d2h, p->ev_chunk[c], 0));

@@ -23,6 +23,31 @@
 
 namespace spamm {
 
+// Waits until every sender's arrival flag has reached wait.epoch, at most wait.limit_ns; on expiry sets *wait.error
+// and goes on (the host then reports the step as failed).  Called by whole blocks.
+__device__ __forceinline__ void peer_wait(const PeerWait &wait)
+{
+    if (!wait.flags) return;
+    if ((int)threadIdx.x < wait.n) {
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+            unsigned int f;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(wait.flags + threadIdx.x) : "memory");
+            if ((int)(f - wait.epoch) >= 0) break;
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > wait.limit_ns) {
+                atomicExch(wait.error, 1);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void peer_wait_selftest_kernel(PeerWait wait) { peer_wait(wait); }
+
 // amax[mi][kc] = max |nA| over tile rows 4mi..4mi+3 and k in chunk kc; bmax[kc][mj] = max |nB| over k in chunk kc and
 // tile columns 8mj..8mj+7.  One warp per output value.
 __global__ void __launch_bounds__(256)
@@ -32,24 +57,7 @@ chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ nor
 {
     // optional: B's norm map is assembled by the other GPUs writing their shares into it; wait (at most 2 s) until
     // every sender's flag has reached this step's number
-    if (wait.flags) {
-        if ((int)threadIdx.x < wait.n) {
-            unsigned long long t0;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-            for (;;) {
-                unsigned int f;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(wait.flags + threadIdx.x) : "memory");
-                if ((int)(f - wait.epoch) >= 0) break;
-                unsigned long long t1;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                if (t1 - t0 > 2000000000ull) {
-                    atomicExch(wait.error, 1);
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-    }
+    peer_wait(wait);
     // optional: zero the counters and need flags the list builder (the next kernel) starts from
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < clear_vecs; i += (size_t)gridDim.x * blockDim.x)
         clear[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -278,6 +286,13 @@ extern "C" size_t spamm_build_lists_scratch_bytes(int row_tiles, int k_tiles, in
     if (row_tiles < 0 || k_tiles < 0 || n_tiles < 0) return 0;
     const size_t kc_n = (size_t)(k_tiles + 31) / 32;
     return sizeof(float) * kc_n * ((size_t)ceil_div(row_tiles, MT_R) + ceil_div(n_tiles, MT_C)) + 16;
+}
+
+int spamm::peer_wait_selftest_launch(const PeerWait &w, cudaStream_t stream)
+{
+    peer_wait_selftest_kernel<<<1, 32, 0, stream>>>(w);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
 }
 
 int spamm::build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,

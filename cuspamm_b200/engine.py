@@ -331,6 +331,9 @@ class ShardedSpamm:
 
     def run(self, tau: float) -> None:
         """norm maps (B's shared between the ranks), lists, pack, multiply; asynchronous."""
+        if self.world == 1 and hasattr(self.plan, "run"):
+            self.plan.run(tau)
+            return
         if self._share is None:
             self.plan.norms()
         elif self._push:

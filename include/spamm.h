@@ -153,6 +153,12 @@ int spamm_norm_a(spamm_plan *plan);
 int spamm_peer_handles(spamm_plan *plan, void *out, size_t out_bytes);
 int spamm_peer_attach(spamm_plan *plan, int world, int rank, const void *all_handles);
 int spamm_norm_b_share_push(spamm_plan *plan, int b_tile_begin, int b_tile_count);
+/*
+ * Exercises the bounded device-side wait of the exchange on one GPU: a small kernel waits for arrival flags of
+ * `senders` GPUs that nothing will ever set, gives up after limit_ms (1..5000) and reports it.  Returns
+ * SPAMM_ERR_DEVICE_WAIT when the wait ran out as it should (the plan stays usable), SPAMM_OK if it did not.
+ */
+int spamm_peer_wait_selftest(spamm_plan *plan, int senders, unsigned int limit_ms);
 
 /* Waits for the plan's stream, then reports a device-side wait that ran out (SPAMM_ERR_DEVICE_WAIT) or SPAMM_OK. */
 int spamm_sync(spamm_plan *plan);

@@ -140,3 +140,25 @@ def test_pipelined_host_to_host_multiply(oracle, chunk_tiles):
         assert np.array_equal(offs, o2) and np.array_equal(kidx, k2)
         assert st["packed_tiles_a"] == int((nA[:, :, None] * nB[None] >= np.float32(tau)).any(axis=2).sum())
         assert st["packed_tiles_b"] == int((nA[:, :, None] * nB[None] >= np.float32(tau)).any(axis=0).sum())
+
+
+def test_bounded_device_wait_reports_and_leaves_the_plan_usable(oracle):
+    """Failure detection without a GPU fault: a device-side wait on flags that nothing sets must give up after its
+    limit, come back as SPAMM_ERR_DEVICE_WAIT, and the same plan must still compute correctly afterwards."""
+    import time
+
+    from cuspamm_b200 import SpammPlan, _lib
+
+    lib = _lib.load()
+    n = 256
+    A = signed_decay(n, 0.05, seed=51)
+    B = signed_decay(n, 0.06, seed=52)
+    with SpammPlan(n, n, n) as p:
+        t0 = time.perf_counter()
+        st = lib.spamm_peer_wait_selftest(p._h, 4, 200)
+        dt = time.perf_counter() - t0
+        assert st == 4, "the wait did not run out"           # SPAMM_ERR_DEVICE_WAIT
+        assert 0.15 < dt < 2.0
+        C, stats = p.multiply(A, B, 0.3)
+    C_ref, S = oracle.spamm(A, B, 0.3)
+    assert stats["survivors"] == S and rel_fro(C, C_ref) <= C_TOL
