@@ -5,7 +5,8 @@
 # The reference fixes its sizes at compile time (para.h:6-8), so the sources are copied to a scratch directory,
 # the three size constants of para.h are set there, and ref_wrap.cu (launchers only) is compiled next to them.
 # Nothing of the reference is written into this repository; oracle/_ref/ holds build outputs only and is
-# git-ignored.  Needs /root/reference (or $SPAMM_REFERENCE_DIR) and nvcc; does nothing otherwise.
+# git-ignored.  Needs the reference sources ($SPAMM_REFERENCE_DIR, or the default below) and nvcc; does nothing
+# when they are absent.
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 REF="${SPAMM_REFERENCE_DIR:-/root/reference}"
