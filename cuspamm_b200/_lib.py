@@ -66,6 +66,9 @@ SIGNATURES = {
     "spamm_get_norm_b": (_i, [_vp, _vp]),
     "spamm_get_counts": (_i, [_vp, _vp, C.POINTER(_i64)]),
     "spamm_get_lists": (_i, [_vp, _vp, _vp]),
+    "spamm_error_norms": (_i, [_vp, _vp, C.POINTER(C.c_double)]),
+    "spamm_error_norms_scratch_bytes": (_sz, []),
+    "spamm_error_norms_dev": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _vp]),
     "spamm_count_valid": (_i, [_vp, _f, C.POINTER(_i64), C.POINTER(C.c_double)]),
     "spamm_tune_tau": (_i, [_vp, C.c_double, _i, C.c_double, C.POINTER(_f), C.POINTER(C.c_double), C.POINTER(_i)]),
     "spamm_count_valid_scratch_bytes": (_sz, [_i, _i]),

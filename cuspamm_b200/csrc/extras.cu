@@ -133,6 +133,79 @@ extern "C" int spamm_count_valid_dev(const float *d_norm_a, const float *d_norm_
 }
 
 // ------------------------------------------------------------------------------------------------------------------
+// Error norms against a reference product: the three Frobenius norms the reference prints with COUNTERRTRANS
+// (tool.cu:6-24, called from check_simple_gpu, tool.cu:227-280): ||ref - C||_F, ||ref||_F, ||C||_F.  Sums of squares
+// in double, block partials first and one block adding them in index order, so the result is reproducible.
+namespace spamm {
+
+struct ErrPartial {
+    double diff, ref, own;
+};
+
+__global__ void __launch_bounds__(256)
+error_norms_kernel(const float4 *__restrict__ ref, const float4 *__restrict__ own, size_t vecs,
+                   ErrPartial *__restrict__ partials)
+{
+    double d = 0.0, r = 0.0, o = 0.0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 a = ref[i], b = own[i];
+        const float e0 = a.x - b.x, e1 = a.y - b.y, e2 = a.z - b.z, e3 = a.w - b.w;
+        d += (double)e0 * e0 + (double)e1 * e1 + (double)e2 * e2 + (double)e3 * e3;
+        r += (double)a.x * a.x + (double)a.y * a.y + (double)a.z * a.z + (double)a.w * a.w;
+        o += (double)b.x * b.x + (double)b.y * b.y + (double)b.z * b.z + (double)b.w * b.w;
+    }
+    __shared__ double sd[256], sr[256], so[256];
+    sd[threadIdx.x] = d; sr[threadIdx.x] = r; so[threadIdx.x] = o;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) {
+            sd[threadIdx.x] += sd[threadIdx.x + s];
+            sr[threadIdx.x] += sr[threadIdx.x + s];
+            so[threadIdx.x] += so[threadIdx.x + s];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partials[blockIdx.x] = ErrPartial{sd[0], sr[0], so[0]};
+}
+
+__global__ void error_norms_finish_kernel(const ErrPartial *__restrict__ partials, int n, double *__restrict__ out)
+{
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        double d = 0.0, r = 0.0, o = 0.0;
+        for (int i = 0; i < n; i++) {
+            d += partials[i].diff;
+            r += partials[i].ref;
+            o += partials[i].own;
+        }
+        out[0] = sqrt(d);
+        out[1] = sqrt(r);
+        out[2] = sqrt(o);
+    }
+}
+
+constexpr int ERR_BLOCKS = 148 * 4;
+
+}  // namespace spamm
+
+extern "C" size_t spamm_error_norms_scratch_bytes(void) { return sizeof(ErrPartial) * ERR_BLOCKS; }
+
+extern "C" int spamm_error_norms_dev(const float *d_ref, const float *d_own, size_t elements, void *d_scratch,
+                                     size_t scratch_bytes, double *d_out3, void *stream)
+{
+    if (!d_ref || !d_own || !d_scratch || !d_out3 || (elements & 3) || scratch_bytes < spamm_error_norms_scratch_bytes() ||
+        (reinterpret_cast<uintptr_t>(d_ref) & 15) || (reinterpret_cast<uintptr_t>(d_own) & 15) ||
+        (reinterpret_cast<uintptr_t>(d_scratch) & 7))
+        return SPAMM_ERR_INVALID;
+    error_norms_kernel<<<ERR_BLOCKS, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float4 *>(d_ref), reinterpret_cast<const float4 *>(d_own), elements / 4,
+        static_cast<ErrPartial *>(d_scratch));
+    error_norms_finish_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(static_cast<ErrPartial *>(d_scratch), ERR_BLOCKS,
+                                                                 d_out3);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // The same count for callers that must not allocate device memory.
 //
 // Some hosts of this library cannot call cudaMalloc when they need a count: a process whose framework has already

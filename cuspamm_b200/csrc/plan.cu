@@ -53,6 +53,7 @@ struct spamm_plan {
     DeviceScalars *h_scalars = nullptr; // pinned
     void *d_cv_scratch = nullptr;       // partial sums of the valid-product counter
     size_t cv_scratch_bytes = 0;
+    void *d_err_scratch = nullptr;      // block partials + 3 doubles of spamm_error_norms
     unsigned long long *d_cv_count = nullptr;   // [count, sum(double)] on the device
     unsigned long long *h_cv = nullptr;         // pinned mirror of the two
     cudaEvent_t ev[8] = {};
@@ -277,6 +278,7 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     p->cv_scratch_bytes = spamm_count_valid_scratch_bytes(p->row_tiles, p->n_tiles);
     if ((st = dev_alloc(&p->d_cv_scratch, p->cv_scratch_bytes))) return fail(st);
     if ((st = dev_alloc(&p->d_cv_count, 16))) return fail(st);
+    if ((st = dev_alloc(&p->d_err_scratch, spamm_error_norms_scratch_bytes() + 32))) return fail(st);
     if (cudaMallocHost(reinterpret_cast<void **>(&p->h_scalars), sizeof(DeviceScalars) * MAX_CHUNKS) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
     if (cudaMallocHost(reinterpret_cast<void **>(&p->h_cv), 16) != cudaSuccess)
@@ -304,7 +306,7 @@ int spamm_plan_destroy(spamm_plan *p)
     cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
     cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared); cudaFree(p->d_order);
     cudaFree(p->d_busy); cudaFree(p->d_tile_list); cudaFree(p->d_list_scratch);
-    cudaFree(p->d_cv_scratch); cudaFree(p->d_cv_count);
+    cudaFree(p->d_cv_scratch); cudaFree(p->d_cv_count); cudaFree(p->d_err_scratch);
     if (p->h_scalars) cudaFreeHost(p->h_scalars);
     if (p->h_cv) cudaFreeHost(p->h_cv);
     for (auto &e : p->ev)
@@ -826,6 +828,23 @@ int spamm_macro_tile_order(int row_tiles, int n_tiles, int32_t *order)
     for (int i0 = 0; i0 < mi_n; i0 += band)
         for (int j = 0; j < mj_n; j++)
             for (int i = i0; i < i0 + band && i < mi_n; i++) order[n++] = i * mj_n + j;
+    return SPAMM_OK;
+}
+
+int spamm_error_norms(spamm_plan *p, const float *d_reference, double out3[3])
+{
+    if (!p || !d_reference || !out3) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    out3[0] = out3[1] = out3[2] = 0.0;
+    if (p->row_tiles == 0) return SPAMM_OK;
+    const size_t part = spamm_error_norms_scratch_bytes();
+    double *d_out = reinterpret_cast<double *>(static_cast<char *>(p->d_err_scratch) + part);
+    int st = spamm_error_norms_dev(d_reference, p->d_c, (size_t)p->row_tiles * TILE * p->N, p->d_err_scratch, part, d_out,
+                                   p->stream);
+    if (st) return st;
+    p->launches += 2;
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(out3, d_out, 3 * sizeof(double), cudaMemcpyDeviceToHost, p->stream));
+    SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
     return SPAMM_OK;
 }
 

@@ -43,6 +43,18 @@ def _host_ptr(x, nbytes: Optional[int] = None) -> int:
     raise TypeError("expected a numpy array or a CPU torch tensor")
 
 
+def pad_to_tiles(x: np.ndarray) -> np.ndarray:
+    """Zero-pads a float32 matrix to multiples of 32 in both dimensions, the reference's padded sizes
+    (main.h:54-56; the reference leaves the padding uninitialised, zeros make it harmless)."""
+    r, c = x.shape
+    R, Cc = -(-r // TILE) * TILE, -(-c // TILE) * TILE
+    if (R, Cc) == (r, c) and x.dtype == np.float32 and x.flags["C_CONTIGUOUS"]:
+        return x
+    out = np.zeros((R, Cc), dtype=np.float32)
+    out[:r, :c] = x
+    return out
+
+
 def row_blocks(row_tiles: int, world: int) -> list:
     """Contiguous blocks of C tile rows, one per GPU, as the reference splits them (cuSpAMM.cu:503,530:
     device d owns tile rows [d*T/G, (d+1)*T/G)).  Boundaries fall on multiples of 4 tile rows (one macro tile)
@@ -214,6 +226,12 @@ class SpammPlan:
         k_idx = np.empty(max(int(offsets[-1]), 1), dtype=np.int32)
         check(self._lib.spamm_get_lists(self._h, offsets.ctypes.data, k_idx.ctypes.data), "spamm_get_lists")
         return offsets, k_idx[: int(offsets[-1])]
+
+    def error_norms(self, d_reference_ptr: int) -> Tuple[float, float, float]:
+        """(||ref - C||_F, ||ref||_F, ||C||_F) against a device matrix of C's shape (tool.cu:6-24)."""
+        out = (C.c_double * 3)()
+        check(self._lib.spamm_error_norms(self._h, C.c_void_p(d_reference_ptr), out), "spamm_error_norms")
+        return float(out[0]), float(out[1]), float(out[2])
 
     def count_valid(self, tau: float) -> Tuple[int, float]:
         """(count, sum of norm products): countValid of the reference (tool.cu:493-529) on the GPU."""

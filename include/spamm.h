@@ -205,6 +205,13 @@ int spamm_get_lists(spamm_plan *plan, int64_t *offsets, int32_t *k_idx);
  */
 int spamm_count_valid(spamm_plan *plan, float tau, int64_t *count, double *sum_of_products);
 /*
+ * The three Frobenius norms the reference's comparator prints (COUNTERRTRANS, tool.cu:6-24, used by
+ * check_simple_gpu, tool.cu:227-280): out3 = { ||ref - C||, ||ref||, ||C|| } over this plan's rows of C, where
+ * d_reference is a device matrix of the same shape (e.g. the dense product: the same plan run with tau = 0 and its
+ * C copied aside, or a cuBLAS result).  Blocking.
+ */
+int spamm_error_norms(spamm_plan *plan, const float *d_reference, double out3[3]);
+/*
  * Threshold for a wanted valid ratio: the reference's tuneValidRate (tool.cu:438-490) -- first guess the mean norm
  * product, then bisection until |ratio - expected_rate| < tolerance or max_iters passes (ExpectedRate 0.75,
  * TUNINGERROR 0.01, TUNINGTIME 20 in main.h:35-38) -- with every count done on the GPU.  Needs spamm_norms; blocking.
@@ -295,6 +302,11 @@ size_t spamm_count_valid_scratch_bytes(int row_tiles, int n_tiles);
 int spamm_count_valid_dev(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles,
                           float tau, void *d_scratch, size_t scratch_bytes, unsigned long long *d_count,
                           double *d_sum, void *stream);
+
+/* The error norms on caller memory; d_scratch holds spamm_error_norms_scratch_bytes() bytes, d_out3 three doubles. */
+size_t spamm_error_norms_scratch_bytes(void);
+int spamm_error_norms_dev(const float *d_ref, const float *d_own, size_t elements, void *d_scratch,
+                          size_t scratch_bytes, double *d_out3, void *stream);
 
 /*
  * spamm_count_valid_dev without caller scratch and without any allocation.  No counterpart in the reference: it

@@ -136,3 +136,51 @@ def test_config5_dense_uniform_rows_sample():
     for r0 in (0, 4000, 8192 - 256):
         ref = (torch.from_numpy(A[r0:r0 + 256]).cuda().half().float() @ Bh).cpu().numpy()
         assert rel_fro(C[r0:r0 + 256], ref) < 1e-5
+
+
+def test_error_norms_against_dense_product(oracle):
+    """The reference's comparator figures (tool.cu:6-24): ||dense - spamm||, ||dense||, ||spamm|| on the GPU, with the
+    dense product made by the same plan at tau = 0."""
+    import torch
+
+    from cuspamm_b200 import BUF_C, SpammPlan, gen_signed_exp
+
+    n = 2048
+    A, B = gen_signed_exp(0.1, 1, n, n), gen_signed_exp(0.1, 2, n, n)
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        p.run(0.0)
+        p.sync()
+        dense = p.as_tensor(BUF_C).clone()
+        p.run(1e-2)
+        p.sync()
+        e, r, o = p.error_norms(dense.data_ptr())
+        C = p.download_c()
+    D = dense.cpu().numpy().astype(np.float64)
+    assert abs(r - np.linalg.norm(D)) <= 1e-9 * r
+    assert abs(o - np.linalg.norm(C.astype(np.float64))) <= 1e-9 * o
+    assert abs(e - np.linalg.norm(D - C)) <= 1e-9 * max(e, 1e-30) + 1e-12
+    assert 0 < e / r < 0.1                     # tau = 1e-2 drops little of an exponentially decaying product
+
+
+def test_cnn_im2col_shape_with_padding(oracle):
+    """The reference's CNN use case (para.h:19-22): a 64x576 weight matrix times a 576x102400 im2col matrix; with
+    sizes that are not multiples of 32 padded with zeros as main.h:54-56 pads them (here 60x570 and 570x4000)."""
+    from cuspamm_b200 import SpammPlan, pad_to_tiles
+
+    rng = np.random.default_rng(9)
+    W = (rng.standard_normal((64, 576)) * np.exp(-4 * rng.random((64, 576)))).astype(np.float32)
+    X = (rng.standard_normal((576, 102400 // 8)) * np.exp(-4 * rng.random((576, 102400 // 8)))).astype(np.float32)
+    tau = 127.0                                # about the median norm product of these matrices
+    with SpammPlan(64, 576, X.shape[1]) as p:
+        C, st = p.multiply(W, X, tau)
+    C_ref, S = oracle.spamm(W, X, tau)
+    assert st["survivors"] == S and 0 < S < st["tile_products"]
+    assert rel_fro(C, C_ref) <= C_TOL
+    Wp, Xp = pad_to_tiles(W[:60, :570]), pad_to_tiles(X[:570, :4000])
+    assert Wp.shape == (64, 576) and Xp.shape == (576, 4000)
+    with SpammPlan(*Wp.shape, Xp.shape[1]) as p:
+        Cp, st = p.multiply(Wp, Xp, 0.0)
+    dense = W[:60, :570].astype(np.float16).astype(np.float64) @ X[:570, :4000].astype(np.float16).astype(np.float64)
+    assert rel_fro(Cp[:60, :4000], dense) < 1e-5
+    assert not Cp[60:].any()
