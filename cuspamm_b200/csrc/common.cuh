@@ -23,6 +23,9 @@ __host__ __device__ inline uint32_t step_k(uint32_t s) { return s & 0xffffu; }
 __host__ __device__ inline uint32_t step_rows(uint32_t s) { return (s >> 16) & 0xfu; }
 __host__ __device__ inline uint32_t step_cols(uint32_t s) { return (s >> 20) & 0xffu; }
 
+__host__ __device__ inline int step_count_of(int32_t v) { return v & SPAMM_STEPS_MASK; }
+__host__ __device__ inline bool step_list_dense(int32_t v) { return (v & SPAMM_STEPS_DENSE) != 0; }
+
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Records a CUDA error for spamm_last_cuda_error and maps it to a status.
@@ -62,7 +65,11 @@ int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_ti
 int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                           const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                           spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                          int64_t ldc, bool reset_queues, cudaStream_t stream);
+                          int64_t ldc, bool reset_queues, bool try_pairs, cudaStream_t stream);
+
+int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const int32_t *d_step_counts,
+                               spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
+                               int64_t ldc, cudaStream_t stream);
 
 #define SPAMM_CUDA_TRY(call)                                                    \
     do {                                                                        \

@@ -20,7 +20,7 @@
 // Two accumulators (2 x 256 of the 512 tensor-memory columns) let the epilogue of one macro tile overlap the
 // multiplies of the next.  Every wait on an mbarrier is bounded in time; when one runs out the block sets the
 // error word, drains its copies and multiplies, frees its tensor memory and returns.
-#include "common.cuh"
+#include "tc_utils.cuh"
 
 namespace spamm {
 
@@ -40,7 +40,6 @@ constexpr int STEP_BATCH = 32 / SPS * SPS;                   // steps fetched pe
 constexpr int GM_THREADS = 320;                            // producer, MMA, 4 epilogue warps, 4 filler warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = MT_C * TILE;                  // 256
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
 constexpr int SMEM_CTRL_BYTES = 512;
 constexpr int SCHED = 4;                                    // depth of the ring of scheduled macro tiles
 constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 128;
@@ -62,120 +61,6 @@ struct Ctrl {
     uint32_t abort_flag;
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Waits for the phase of `bar` with the given parity to complete, at most WAIT_LIMIT_NS.
-__device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int32_t *err,
-                                       int code)
-{
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            atomicCAS(err, 0, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                             int32_t *err, int code)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    return wait_slow(bar, parity, abort_flag, err, code);
-}
-
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-// K-major, no swizzle: 8-row groups 512 B apart (SBO), the two 8-element k chunks of a K=16 step 128 B apart (LBO).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
-{
-    const uint32_t lo = ((addr & 0x3ffffu) >> 4) | ((128u >> 4) << 16);
-    const uint32_t hi = (512u >> 4) | (1u << 14);
-    return ((uint64_t)hi << 32) | lo;
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, 1, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%4, %5, %6, %7}, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *v)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st32_zero(uint32_t taddr)
-{
-    const uint32_t z = 0;
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
-        "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
-        "r"(z)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Writes one macro tile of C as zeros with `nthreads` threads (a multiple of 64); `t` is the caller's index among them.
 __device__ __forceinline__ void zero_fill_macro_tile(float *__restrict__ c, int64_t ldc, int mi, int mj, int rows_total,
@@ -203,7 +88,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                       const uint32_t *__restrict__ steps, const int32_t *__restrict__ step_counts,
                       const int32_t *__restrict__ order, const int32_t *__restrict__ busy_list,
                       spamm_list_scalars *__restrict__ sc, int row_tiles, int k_tiles, int n_tiles,
-                      float *__restrict__ c, int64_t ldc)
+                      float *__restrict__ c, int64_t ldc, int pairs_launched)
 {
     extern __shared__ uint8_t smem_raw[];
     // stage data first (128-byte aligned), control block after it
@@ -258,6 +143,16 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
     __syncthreads();
     tc_fence_after();
 
+    // Dense macro tiles that have a dense vertical neighbour belong to the paired (two-SM) kernel, which runs first
+    // on the stream whenever at least half of the macro tiles are dense; this kernel leaves them alone.
+    const bool pair_active = pairs_launched && mi_n >= 2 && sc->dense_count * 2u >= n_mt;
+    auto pair_owned = [&](int mt, int raw_count) -> bool {
+        if (!pair_active || !step_list_dense(raw_count)) return false;
+        const int mi = mt / mj_n, partner = mi ^ 1;
+        return partner < mi_n && step_list_dense(step_counts[partner * mj_n + (mt % mj_n)]);
+    };
+    const bool nothing_left = pair_active && sc->pair_done == n_mt;
+
     if (warp == 0) {
         // ------------------------------------------------------------------ scheduler + producer
         // Work queue: macro tiles that have steps come first (they take several times longer than a macro tile
@@ -274,7 +169,9 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         bool ok = true;
         while (ok) {
             int mt = -1, cnt = 0;
-            if (phase == 1) {
+            if (nothing_left) {
+                // every macro tile was multiplied by the paired kernel: publish the end marker and stop
+            } else if (phase == 1) {
                 unsigned int ti = 0;
                 if (lane == 0) ti = atomicAdd(&sc->queue_busy, 1u);
                 ti = __shfl_sync(0xffffffffu, ti, 0);
@@ -284,6 +181,8 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 }
                 mt = busy_list[ti];
                 cnt = step_counts[mt];
+                if (pair_owned(mt, cnt)) continue;
+                cnt = step_count_of(cnt);
             } else {
                 bool exhausted = false;
                 while (!pending && !exhausted) {
@@ -297,8 +196,10 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                     cand_mt = -1;
                     if ((unsigned int)lane < chunk && p0 + lane < n_mt) {
                         cand_mt = order ? order[p0 + lane] : (int)(p0 + lane);
-                        cand_cnt = step_counts[cand_mt];
+                        const int raw = step_counts[cand_mt];
+                        cand_cnt = step_count_of(raw);
                         if (use_busy && cand_cnt > 0) cand_mt = -1;     // already handled in the first phase
+                        else if (pair_owned(cand_mt, raw)) cand_mt = -1;
                     }
                     pending = __ballot_sync(0xffffffffu, cand_mt >= 0);
                 }
@@ -493,7 +394,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         // group of 64 threads that claims four macro tiles at a time from the same counter the scheduler uses for
         // its second phase; the next claim is issued before the current tiles are written.
         const unsigned int busy_n = sc->busy_count;
-        if (busy_n * 4u <= n_mt) {
+        if (busy_n * 4u <= n_mt && !nothing_left) {
             const int pair_lane = threadIdx.x & 63;          // index inside the group of two warps
             const uint32_t bar_id = 1u + (uint32_t)((warp - 6) >> 1);
             volatile int32_t *claim = &ctrl->filler_claim[(warp - 6) >> 1][0];
@@ -506,7 +407,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                     int m = -1;
                     if (p0 + pair_lane < n_mt) {
                         m = order ? order[p0 + pair_lane] : (int)(p0 + pair_lane);
-                        if (step_counts[m] > 0) m = -1;      // handled by the pipeline
+                        if (step_count_of(step_counts[m]) > 0) m = -1;      // handled by the pipeline
                     }
                     claim[pair_lane] = m;
                 }
@@ -600,13 +501,13 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
                                         int k_tiles, int n_tiles, float *d_c, int64_t ldc, void *stream)
 {
     return spamm::gated_multiply_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_order, d_busy_list, d_scalars,
-                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, (cudaStream_t)stream);
+                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, true, (cudaStream_t)stream);
 }
 
 int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                                  const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                                  spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                                 int64_t ldc, bool reset_queues, cudaStream_t stream)
+                                 int64_t ldc, bool reset_queues, bool try_pairs, cudaStream_t stream)
 {
     using namespace spamm;
     if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
@@ -635,10 +536,17 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
     const int sm_count = sm_count_of[dev];
     // the two work counters start from zero at every launch (unless the packing kernel just reset them)
     if (reset_queues) SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 2 * sizeof(unsigned int), stream));
+    // dense macro tiles with a dense vertical neighbour go to pairs of SMs first (a no-op below half dense);
+    // a caller that knows the lists are sparse can save the launch
+    if (try_pairs) {
+        int st = gated_multiply_pair_launch(d_half_a, d_half_b, d_step_counts, d_scalars, row_tiles, k_tiles, n_tiles,
+                                            d_c, ldc, stream);
+        if (st) return st;
+    }
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
     gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, stream>>>(
         static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
-        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc);
+        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, try_pairs ? 1 : 0);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

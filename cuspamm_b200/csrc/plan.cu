@@ -65,6 +65,7 @@ struct spamm_plan {
 
     int active_scalars = 1;
     bool queues_clean = false;
+    int dense_hint = -1;                // last counters read: were at least half of the macro tiles dense (-1: unknown)
     // peer exchange of B's norm-map shares (one process per GPU, see spamm_peer_attach)
     float *d_norm_b_buf[2] = {nullptr, nullptr};   // B's map, double buffered by step parity; d_norm_b is the current
     unsigned int *d_peer_flags = nullptr;          // [MAX_PEERS] arrival flags + [1] block counter of the push kernel
@@ -135,6 +136,11 @@ int read_scalars(spamm_plan *p)
         SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_peer_error, p->d_peer_error, sizeof(int), cudaMemcpyDeviceToHost,
                                        p->stream));
     SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
+    // remember whether these lists were mostly dense: the next multiply launches the paired kernel only then
+    // (a wrong guess costs speed, never correctness: the one-SM kernel is told whether the paired one ran)
+    unsigned long long dense = 0;
+    for (int c = 0; c < p->active_scalars; c++) dense += p->h_scalars[c].dense_count;
+    p->dense_hint = (dense * 2 >= p->n_mt() && p->n_mt() > 0) ? 1 : 0;
     return SPAMM_OK;
 }
 
@@ -517,7 +523,7 @@ int spamm_gated_multiply(spamm_plan *p)
     if (p->row_tiles) {
         int st = gated_multiply_launch(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
                                        p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N,
-                                       !p->queues_clean, p->stream);
+                                       !p->queues_clean, p->dense_hint != 0, p->stream);
         p->queues_clean = false;
         if (st) return st;
         p->launches++;
@@ -578,7 +584,7 @@ static int64_t sum_step_counts(spamm_plan *p, int *status)
         return 0;
     }
     int64_t t = 0;
-    for (int32_t v : sc) t += v;
+    for (int32_t v : sc) t += step_count_of(v);
     return t;
 }
 
@@ -655,7 +661,7 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
         return st;
     if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, stream)))
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->dense_hint != 0, stream)))
         return st;
     p->launches += do_norm ? 5 : 4;
     return SPAMM_OK;
@@ -777,6 +783,7 @@ int spamm_get_lists(spamm_plan *p, int64_t *offsets, int32_t *k_idx)
         SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
     }
     std::vector<size_t> first(n_mt + 1, 0);
+    for (int32_t &v : sc) v = step_count_of(v);
     for (size_t m = 0; m < n_mt; m++) first[m + 1] = first[m] + (size_t)sc[m];
     std::vector<uint32_t> steps(first[n_mt]);
     for (size_t m = 0; m < n_mt; m++) {

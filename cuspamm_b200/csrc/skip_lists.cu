@@ -139,6 +139,7 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
 
     int n_out = 0;       // warp-uniform
     int my_count = 0;    // lane b counts survivors of pair b = column*4 + row
+    int full_k = 0;      // warp-uniform: number of k whose 32 products all survive
 
     // pairs (row r, column c) of this macro tile that exist, bit c*4 + r
     uint32_t valid_bits = 0;
@@ -191,6 +192,7 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
                 mask &= valid_bits;
             }
             if (!__any_sync(0xffffffffu, mask != 0)) continue;
+            full_k += __popc(__ballot_sync(0xffffffffu, mask == 0xffffffffu));
             // per-tile list lengths
 #pragma unroll
             for (int bit = 0; bit < 32; bit++) {
@@ -264,8 +266,11 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
         }
     }
     if (lane == 0) {
-        step_counts[mt] = n_out;
+        // dense: every k is there and each is one step naming all rows and columns
+        const bool dense = k_tiles > 0 && full_k == k_tiles && n_out == k_tiles;
+        step_counts[mt] = n_out | (dense ? SPAMM_STEPS_DENSE : 0);
         if (n_out > 0) busy_list[atomicAdd(&sc->busy_count, 1u)] = mt;
+        if (dense) atomicAdd(&sc->dense_count, 1u);
     }
     {
         const int r = lane & 3, c = lane >> 2;

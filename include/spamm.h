@@ -31,6 +31,8 @@ extern "C" {
 #define SPAMM_TILE 32          /* LoNum, main.h:32 */
 #define SPAMM_MT_ROWS 4        /* C tiles per macro tile, vertically (128 rows)  */
 #define SPAMM_MT_COLS 8        /* C tiles per macro tile, horizontally (256 columns) */
+#define SPAMM_STEPS_DENSE 0x40000000   /* flag bit in a macro tile's step count, see spamm_build_lists_dev */
+#define SPAMM_STEPS_MASK  0x3fffffff
 
 typedef enum spamm_status {
     SPAMM_OK = 0,
@@ -75,6 +77,8 @@ typedef struct spamm_list_scalars {
     unsigned int packed_b;          /* tiles of B converted by the packing kernel */
     unsigned int queue_busy;        /* work counters of the multiply kernel; every multiply call resets the two */
     unsigned int queue_all;
+    unsigned int dense_count;       /* macro tiles whose list has every k with every row and column (list builder) */
+    unsigned int pair_done;         /* macro tiles the paired (two-SM) multiply kernel took care of */
     int32_t overflow;               /* non-zero: a step list did not fit */
     int32_t error;                  /* non-zero: a bounded wait of the multiply kernel ran out (which one) */
 } spamm_list_scalars;
@@ -248,7 +252,8 @@ int spamm_norm_map_pair_dev(const float *d_xa, int rows_a, int cols_a, int64_t l
  * The norm maps must be non-negative (they are norms).
  *   d_scratch      work space of spamm_build_lists_scratch_bytes(...) bytes (chunk maxima used for pruning)
  *   d_steps        8*(K/32) words per macro tile, macro tiles in row-major order
- *   d_step_counts  [macro tiles] number of steps written
+ *   d_step_counts  [macro tiles] number of steps written, in bits 0-29; bit 30 (SPAMM_STEPS_DENSE) is set when the
+ *                  list holds every k and every step names all 4 rows and 8 columns (a dense macro tile)
  *   d_counts       [row_tiles][N/32] per-tile list lengths
  *   d_need_a/_b    one byte per A slab of 4 tiles / B slab of 8 tiles, a bit per tile that some step names;
  *                  zero on entry, or the flags an earlier call on other rows of A left (tiles of B that are flagged
@@ -280,6 +285,9 @@ int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k
 /*
  * Gated multiply (get_C_FP16_B32, cuSpAMM.cu:336-391): walks the step lists, multiplies on the tensor cores
  * (half inputs, float accumulation) and writes every C tile of the block, zeros where a list is empty.
+ * Two kernels are launched: when at least half of the macro tiles are dense, vertically adjacent dense ones are
+ * multiplied by pairs of SMs (one 256 x 256 tensor-core tile per pair); everything else goes through the
+ * one-SM kernel.
  * d_order (may be NULL = row-major) is a permutation of the macro-tile indices: the order in which the resident
  * blocks take macro tiles from the work queue; spamm_macro_tile_order fills one that keeps concurrently processed
  * macro tiles close together in both directions, so that they share operand tiles in L2.  When few macro tiles

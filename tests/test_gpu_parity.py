@@ -162,3 +162,39 @@ def test_bounded_device_wait_reports_and_leaves_the_plan_usable(oracle):
         C, stats = p.multiply(A, B, 0.3)
     C_ref, S = oracle.spamm(A, B, 0.3)
     assert stats["survivors"] == S and rel_fro(C, C_ref) <= C_TOL
+
+
+def test_dense_macro_tiles_with_and_without_the_paired_kernel(oracle):
+    """Dense macro tiles are multiplied by pairs of SMs when the previous lists of the plan were mostly dense, by the
+    one-SM kernel otherwise; the switch is a speed hint and must never change the result."""
+    from cuspamm_b200 import SpammPlan
+
+    n = 768                                       # 6 macro-tile rows: three vertical pairs
+    A = signed_decay(n, 0.002, seed=61)
+    B = signed_decay(n, 0.002, seed=62)
+    C_ref, S = oracle.spamm(A, B, 0.0)
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        results = []
+        for tau in (1e12, 0.0, 0.0, 1e12, 0.0):   # sparse -> dense (hint says sparse) -> dense (hint says dense) -> ...
+            p.run(tau)
+            p.sync()                              # reading the counters refreshes the hint
+            results.append((tau, p.download_c(), p.counts()[1]))
+    for tau, C, s in results:
+        if tau == 0.0:
+            assert s == S == (n // 32) ** 3
+            assert rel_fro(C, C_ref) <= 2e-6
+        else:
+            assert s == 0 and not C.any()
+    # a mixed case: upper half dense, lower half sparse -> pairs only where both neighbours are dense
+    A2 = A.copy()
+    A2[384:] *= np.float32(1e-6)
+    tau = float(np.median(oracle.norm_map(A2)[:, :, None] * oracle.norm_map(B)[None]))
+    C_ref2, S2 = oracle.spamm(A2, B, tau)
+    with SpammPlan(n, n, n) as p:
+        p.upload(A2, B)
+        for _ in range(2):
+            p.run(tau)
+            p.sync()
+            assert p.counts()[1] == S2
+            assert rel_fro(p.download_c(), C_ref2) <= C_TOL
