@@ -34,8 +34,18 @@ SEED_A, SEED_B = 1, 2
 SWEEP_TAUS = [0.0, 1e-10, 1e-6, 1e-4, 1e-2]
 
 
+# The benchmark configurations of BASELINE.json: name -> (description, default N, default tau)
+WORKLOADS = {
+    "exp": ("a_ij=+-exp(-0.1|i-j|), seeds 1/2", 16384, 1e-6),            # the headline (config 2 family at N=16384)
+    "alg": ("a_ij=u_ij/(|i-j|^2+1), u in [-1,1), seeds 3/4", 16384, 1e-6),   # config 3
+    "lattice": ("a_ij=+-u*exp(-|r_i-r_j|) on an L^3 grid, u in [0.5,1), symmetric, seed 7, A=B", 32768, 1e-8),  # config 4
+    "dense": ("a_ij uniform in [-1,1), seeds 5/6", 16384, 0.0),            # config 5
+}
+WORKLOAD = ["exp"]
+
+
 def workload_name(n: int, tau: float) -> str:
-    return f"N={n} fp32 A,B: a_ij=+-exp(-{LAMBDA}|i-j|), seeds {SEED_A}/{SEED_B}, tile 32, tau={tau:g}"
+    return f"N={n} fp32 A,B: {WORKLOADS[WORKLOAD[0]][0]}, tile 32, tau={tau:g}"
 
 
 def read_peaks() -> dict:
@@ -125,11 +135,24 @@ def pinned(shape):
 
 
 def generate_into(arr: np.ndarray, seed: int, row_begin: int, cols: int) -> None:
+    """Rows [row_begin, row_begin+rows) of operand `seed` (SEED_A or SEED_B) of the selected workload."""
     from cuspamm_b200 import _lib
 
     lib = _lib.load()
-    _lib.check(lib.spamm_gen_signed_exp(arr.ctypes.data, LAMBDA, seed, row_begin, arr.shape[0], cols),
-               "spamm_gen_signed_exp")
+    w, p, rows = WORKLOAD[0], arr.ctypes.data, arr.shape[0]
+    first = seed == SEED_A
+    if w == "exp":
+        st = lib.spamm_gen_signed_exp(p, LAMBDA, seed, row_begin, rows, cols)
+    elif w == "alg":
+        st = lib.spamm_gen_uniform_alg(p, 3 if first else 4, row_begin, rows, cols)
+    elif w == "dense":
+        st = lib.spamm_gen_uniform(p, 5 if first else 6, row_begin, rows, cols)
+    else:
+        L = round(cols ** (1.0 / 3.0))
+        if L ** 3 != cols:
+            raise SystemExit("the lattice workload needs N = L^3 (e.g. 32768 = 32^3, 4096 = 16^3)")
+        st = lib.spamm_gen_lattice(p, L, 7, row_begin, rows)
+    _lib.check(st, "generator")
 
 
 # ------------------------------------------------------------------------------------------------ CPU leg
@@ -379,7 +402,9 @@ def run_ours(args):
                                     "peak": peaks["tflops_sustained"],
                                     "frac": dense[0]["multiply_tflops"] / peaks["tflops_sustained"],
                                     "note": "tau=0: every tile product executed; multiply kernel alone"}
-    if world == 1 and not args.no_cpu:
+    if world == 1 and not args.no_cpu and S * 32768.0 > 1.0e11:
+        line["cpu_baseline"] = {"skipped": f"{S * 32768.0:.2e} scalar multiply-adds: hours on the host cores"}
+    elif world == 1 and not args.no_cpu:
         try:
             from oracle import oracle as O
 
@@ -411,13 +436,21 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--n", type=int, default=16384)
-    ap.add_argument("--tau", type=float, default=1e-6)
+    ap.add_argument("--workload", default="exp", choices=sorted(WORKLOADS))
+    ap.add_argument("--n", type=int, default=None)
+    ap.add_argument("--tau", type=float, default=None)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--exchange", default="nccl", choices=["push", "nccl"],
                     help="multi-GPU: how B's norm-map shares travel (peer stores from the norm kernel, or NCCL all-gather)")
     args = ap.parse_args()
+    WORKLOAD[0] = args.workload
+    if args.n is None:
+        args.n = WORKLOADS[args.workload][1]
+    if args.tau is None:
+        args.tau = WORKLOADS[args.workload][2]
+    if args.workload != "exp":
+        args.no_sweep = True          # the tau sweep belongs to the headline workload
     if args.impl == "reference":
         run_reference_arm(args)
     else:

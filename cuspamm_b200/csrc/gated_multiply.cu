@@ -24,7 +24,9 @@
 
 namespace spamm {
 
-// A stage of the ring holds the operands of up to SPS consecutive steps of one macro tile.  The thread that issues the
+// A stage of the ring holds SPS slots; a slot holds the operands of ONE k of one macro tile (8 KiB of A, 16 KiB of B)
+// and up to GSTEPS steps of that k (steps of the same k differ only in which rows and columns take part, so they
+// share the slab copies).  The thread that issues the
 // multiplies pays a fixed price per stage (barrier wait, commit) and about 110 cycles per tcgen05.mma, against 128
 // cycles of tensor-pipe time for an N=256 instruction, so several steps share one wait and one commit.
 #ifndef SPAMM_SPS
@@ -36,13 +38,13 @@ constexpr int STAGE_BYTES = SPS * (A_SLAB_BYTES + B_SLAB_BYTES);   // 24 KiB per
 #define SPAMM_STAGES (8 / SPAMM_SPS)
 #endif
 constexpr int STAGES = SPAMM_STAGES;
-constexpr int STEP_BATCH = 32 / SPS * SPS;                   // steps fetched per warp-wide read of the list
+constexpr int GSTEPS = 4;                                    // steps of one k that share a stage slot (more: next slot)
 constexpr int GM_THREADS = 320;                            // producer, MMA, 4 epilogue warps, 4 filler warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = MT_C * TILE;                  // 256
-constexpr int SMEM_CTRL_BYTES = 512;
+constexpr int SMEM_CTRL_BYTES = 640;
 constexpr int SCHED = 4;                                    // depth of the ring of scheduled macro tiles
-constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 128;
+constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 4 * EPI_WARP_BYTES + 128;
 
 struct Ctrl {
     unsigned long long full[STAGES];
@@ -56,7 +58,8 @@ struct Ctrl {
     uint32_t filler_base[2];
     int32_t tile_slot[SCHED];
     int32_t tile_cnt[SCHED];
-    uint32_t step_word[STAGES][SPS];
+    uint32_t step_word[STAGES][SPS][GSTEPS];                  // per stage slot: the steps of one k, zero terminated
+    uint32_t stage_last[STAGES];                               // this stage ends its macro tile
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -228,77 +231,95 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             const uint32_t *list = steps + (int64_t)mt * cap;
             const uint8_t *a_base = half_a + (int64_t)mi * k_tiles * A_SLAB_BYTES;
             const uint8_t *b_base = half_b + (int64_t)mj * B_SLAB_BYTES;
-            uint32_t next = (lane < STEP_BATCH && lane < cnt) ? __ldg(list + lane) : 0u;
-            for (int i0 = 0; i0 < cnt && ok; i0 += STEP_BATCH) {
+            // lane 0 assembles stages: consecutive steps with the same k go to one slot and share one copy of the A
+            // slab and one of the B columns they span; a stage is sent off when its slots are full or the list ends
+            uint32_t sw[SPS][GSTEPS];
+            uint32_t rows_u[SPS], cols_u[SPS];
+            int n_slots = 0, n_in_slot = 0;
+            auto flush_stage = [&](bool last) {
+                const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
+                ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, ERR_WAIT_EMPTY);
+                if (!ok) return;
+                const uint32_t bar = smem_u32(&ctrl->full[s]);
+                const uint32_t a_stage = smem_u32(smem + s * STAGE_BYTES);
+                const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+                uint32_t bytes = 0;
+                uint32_t a_bytes[SPS], b_first[SPS], b_len[SPS];
+#pragma unroll
+                for (int t = 0; t < SPS; t++) {
+#pragma unroll
+                    for (int g = 0; g < GSTEPS; g++) ctrl->step_word[s][t][g] = (t < n_slots) ? sw[t][g] : 0u;
+                    a_bytes[t] = b_first[t] = b_len[t] = 0;
+                    if (t < n_slots) {
+                        // A: one tile when a single row takes part, else the whole slab in one copy
+                        a_bytes[t] = (__popc(rows_u[t]) == 1) ? TILE_BYTES : A_SLAB_BYTES;
+                        // B: everything from the first to the last column that takes part, in one copy
+                        b_first[t] = (uint32_t)(__ffs(cols_u[t]) - 1);
+                        b_len[t] = (uint32_t)(32 - __clz(cols_u[t])) - b_first[t];
+                        bytes += a_bytes[t] + b_len[t] * TILE_BYTES;
+                    }
+                }
+                ctrl->stage_last[s] = last ? 1u : 0u;
+                mbar_arrive_expect_tx(bar, bytes);
+                bool a_done = false;
+                if (SPS >= 2 && n_slots >= 2 && a_bytes[0] == A_SLAB_BYTES && a_bytes[1] == A_SLAB_BYTES &&
+                    step_k(sw[1][0]) == step_k(sw[0][0]) + 1u) {
+                    // two slabs of consecutive k are neighbours in memory
+                    bulk_g2s(a_stage, a_base + (int64_t)step_k(sw[0][0]) * A_SLAB_BYTES, 2 * A_SLAB_BYTES, bar);
+                    a_done = true;
+                }
+#pragma unroll
+                for (int t = 0; t < SPS; t++) {
+                    if (t >= n_slots) break;
+                    const uint32_t k = step_k(sw[t][0]);
+                    const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
+                    const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
+                    if (a_done && t < 2) {
+                    } else if (a_bytes[t] == A_SLAB_BYTES) {
+                        bulk_g2s(a_stage + t * A_SLAB_BYTES, a_src, A_SLAB_BYTES, bar);
+                    } else {
+                        const uint32_t q = (uint32_t)(__ffs(rows_u[t]) - 1);
+                        bulk_g2s(a_stage + t * A_SLAB_BYTES + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
+                    }
+                    bulk_g2s(b_stage + t * B_SLAB_BYTES + b_first[t] * TILE_BYTES, b_src + b_first[t] * TILE_BYTES,
+                             b_len[t] * TILE_BYTES, bar);
+                }
+                slot++;
+                n_slots = 0;
+                n_in_slot = 0;
+            };
+            uint32_t next = (lane < cnt) ? __ldg(list + lane) : 0u;
+            for (int i0 = 0; i0 < cnt && ok; i0 += 32) {
                 const uint32_t mine = next;
                 // fetch the following batch of steps while these are being issued
-                next = (lane < STEP_BATCH && i0 + STEP_BATCH + lane < cnt) ? __ldg(list + i0 + STEP_BATCH + lane) : 0u;
-                const int nb = min(STEP_BATCH, cnt - i0);
-                for (int j = 0; j < nb; j += SPS) {
-                    uint32_t w[SPS];
-#pragma unroll
-                    for (int t = 0; t < SPS; t++) {
-                        w[t] = __shfl_sync(0xffffffffu, mine, (j + t) & 31);
-                        if (j + t >= nb) w[t] = 0u;              // a step word is never zero (its row set is not empty)
-                    }
+                next = (i0 + 32 + lane < cnt) ? __ldg(list + i0 + 32 + lane) : 0u;
+                const int nb = min(32, cnt - i0);
+                for (int j = 0; j < nb; j++) {
+                    const uint32_t w = __shfl_sync(0xffffffffu, mine, j);
                     if (lane == 0) {
-                        const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
-                        ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, ERR_WAIT_EMPTY);
+                        const bool same_k = n_in_slot > 0 && n_in_slot < GSTEPS && step_k(sw[n_slots - 1][0]) == step_k(w);
+                        if (!same_k) {
+                            if (n_slots == SPS) flush_stage(false);
+                            if (ok) {
+                                n_slots++;
+                                n_in_slot = 0;
+                                rows_u[n_slots - 1] = cols_u[n_slots - 1] = 0;
+#pragma unroll
+                                for (int g = 0; g < GSTEPS; g++) sw[n_slots - 1][g] = 0u;
+                            }
+                        }
                         if (ok) {
-                            const uint32_t bar = smem_u32(&ctrl->full[s]);
-                            const uint32_t a_stage = smem_u32(smem + s * STAGE_BYTES);
-                            const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
-                            uint32_t tiles = 0;
-#pragma unroll
-                            for (int t = 0; t < SPS; t++) {
-                                ctrl->step_word[s][t] = w[t];
-                                tiles += __popc(w[t] >> 16);       // rows and columns named by the step
-                            }
-                            mbar_arrive_expect_tx(bar, tiles * TILE_BYTES);
-                            bool a_done = false;
-                            if (SPS >= 2 && (w[0] >> 16) == 0xfffu && (w[1] >> 16) == 0xfffu &&
-                                step_k(w[1]) == step_k(w[0]) + 1u) {
-                                // two full steps with consecutive k: their A slabs are neighbours in memory
-                                bulk_g2s(a_stage, a_base + (int64_t)step_k(w[0]) * A_SLAB_BYTES, 2 * A_SLAB_BYTES, bar);
-                                a_done = true;
-                            }
-#pragma unroll
-                            for (int t = 0; t < SPS; t++) {
-                                if (w[t] == 0u) break;
-                                const uint32_t k = step_k(w[t]), rows = step_rows(w[t]), cols = step_cols(w[t]);
-                                const uint32_t a_dst = a_stage + t * A_SLAB_BYTES;
-                                const uint32_t b_dst = b_stage + t * B_SLAB_BYTES;
-                                const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
-                                const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
-                                if (a_done && t < 2) {
-                                } else if (rows == 0xfu) {
-                                    bulk_g2s(a_dst, a_src, A_SLAB_BYTES, bar);
-                                } else {
-#pragma unroll
-                                    for (int q = 0; q < MT_R; q++)
-                                        if ((rows >> q) & 1u)
-                                            bulk_g2s(a_dst + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
-                                }
-                                if (cols == 0xffu) {
-                                    bulk_g2s(b_dst, b_src, B_SLAB_BYTES, bar);
-                                } else {
-                                    uint32_t rest = cols;
-                                    while (rest) {
-                                        const int c0 = __ffs(rest) - 1;
-                                        const uint32_t shifted = rest >> c0;
-                                        const int len = __ffs(~shifted) - 1;   // run of ones starting at c0
-                                        bulk_g2s(b_dst + c0 * TILE_BYTES, b_src + c0 * TILE_BYTES, len * TILE_BYTES, bar);
-                                        rest &= ~(((1u << len) - 1u) << c0);
-                                    }
-                                }
-                            }
-                            slot++;
+                            sw[n_slots - 1][n_in_slot++] = w;
+                            rows_u[n_slots - 1] |= step_rows(w);
+                            cols_u[n_slots - 1] |= step_cols(w);
                         }
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                 }
             }
+            if (lane == 0 && ok && n_slots > 0) flush_stage(true);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         if (lane == 0 && *abort_flag) {
             // make sure every copy this block issued has landed before the block can exit
@@ -333,42 +354,45 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t dbase = tmem_base + buf * ACC_COLS;
-                const int n_groups = (cnt + SPS - 1) / SPS;
-                for (int g = 0; g < n_groups; g++) {
+                for (bool last = false; !last;) {
                     const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
                     ok = wait_bounded(smem_u32(&ctrl->full[s]), ph, abort_flag, err, ERR_WAIT_FULL);
                     if (!ok) break;
                     tc_fence_after();
+                    last = ctrl->stage_last[s] != 0u;
                     const uint32_t a_stage = stage0 + s * STAGE_BYTES;
                     const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
 #pragma unroll
                     for (int t = 0; t < SPS; t++) {
-                        const uint32_t w = ctrl->step_word[s][t];
-                        if (w == 0u) break;
                         const uint32_t a_addr = a_stage + t * A_SLAB_BYTES;
                         const uint32_t b_addr = b_stage + t * B_SLAB_BYTES;
-                        if ((w >> 16) == 0xfffu) {
-                            // every row and every column of the macro tile: two instructions with N = 256
-                            const uint64_t da = desc0 + (uint64_t)(a_addr >> 4), db = desc0 + (uint64_t)(b_addr >> 4);
-                            umma_f16(dbase, da, db, IDESC_N256, 0u, 0u, 0u, 0u);
-                            umma_f16(dbase, da + 16u, db + 16u, IDESC_N256, 0u, 0u, 0u, 0u);
-                        } else {
-                            const uint32_t rows = step_rows(w), cols = step_cols(w);
-                            const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
-                            const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
-                            uint32_t rest = cols;
-                            while (rest) {
-                                const int c0 = __ffs(rest) - 1;
-                                const uint32_t shifted = rest >> c0;
-                                const int len = __ffs(~shifted) - 1;
-                                const uint32_t n = (uint32_t)len * TILE;
-                                const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-                                const uint64_t da = desc0 + (uint64_t)(a_addr >> 4);
-                                const uint64_t db = desc0 + (uint64_t)((b_addr + (uint32_t)c0 * TILE_BYTES) >> 4);
-                                const uint32_t dcol = dbase + (uint32_t)c0 * TILE;
-                                umma_f16(dcol, da, db, idesc, m0, m1, m2, m3);
-                                umma_f16(dcol, da + 16u, db + 16u, idesc, m0, m1, m2, m3);
-                                rest &= ~(((1u << len) - 1u) << c0);
+                        const uint64_t da = desc0 + (uint64_t)(a_addr >> 4);
+#pragma unroll 1
+                        for (int g = 0; g < GSTEPS; g++) {
+                            const uint32_t w = ctrl->step_word[s][t][g];
+                            if (w == 0u) break;
+                            if ((w >> 16) == 0xfffu) {
+                                // every row and every column of the macro tile: two instructions with N = 256
+                                const uint64_t db = desc0 + (uint64_t)(b_addr >> 4);
+                                umma_f16(dbase, da, db, IDESC_N256, 0u, 0u, 0u, 0u);
+                                umma_f16(dbase, da + 16u, db + 16u, IDESC_N256, 0u, 0u, 0u, 0u);
+                            } else {
+                                const uint32_t rows = step_rows(w), cols = step_cols(w);
+                                const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
+                                const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
+                                uint32_t rest = cols;
+                                while (rest) {
+                                    const int c0 = __ffs(rest) - 1;
+                                    const uint32_t shifted = rest >> c0;
+                                    const int len = __ffs(~shifted) - 1;
+                                    const uint32_t n = (uint32_t)len * TILE;
+                                    const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+                                    const uint64_t db = desc0 + (uint64_t)((b_addr + (uint32_t)c0 * TILE_BYTES) >> 4);
+                                    const uint32_t dcol = dbase + (uint32_t)c0 * TILE;
+                                    umma_f16(dcol, da, db, idesc, m0, m1, m2, m3);
+                                    umma_f16(dcol, da + 16u, db + 16u, idesc, m0, m1, m2, m3);
+                                    rest &= ~(((1u << len) - 1u) << c0);
+                                }
                             }
                         }
                     }
@@ -432,6 +456,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         // ------------------------------------------------------------------ epilogue (4 warps)
         const uint32_t q = (uint32_t)(warp & 3);
         const int e = threadIdx.x - 64;
+        uint8_t *epi_tile = smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + (warp - 2) * EPI_WARP_BYTES;
         uint32_t acc_iter = 0;
         bool ok = true;
         for (uint32_t sidx = 0; ok; sidx++) {
@@ -457,7 +482,8 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             tc_fence_after();
             const int row = mi * (MT_R * TILE) + (int)q * TILE + lane;
             const bool row_ok = row < rows_total;
-            float *crow = c + (int64_t)row * ldc + (int64_t)mj * (MT_C * TILE);
+            // first row of this warp's 32-row block of C, first column of the macro tile
+            float *cblock = c + (int64_t)(row - lane) * ldc + (int64_t)mj * (MT_C * TILE);
 #pragma unroll 1
             for (int cc = 0; cc < MT_C; cc++) {
                 const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS + (uint32_t)cc * TILE;
@@ -465,17 +491,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 tmem_ld32(taddr, v);
                 tmem_wait_ld();
                 tmem_st32_zero(taddr);
-                if (row_ok && mj * MT_C + cc < n_tiles) {
-#pragma unroll
-                    for (int x = 0; x < 8; x++) {
-                        float4 o;
-                        o.x = __uint_as_float(v[4 * x + 0]);
-                        o.y = __uint_as_float(v[4 * x + 1]);
-                        o.z = __uint_as_float(v[4 * x + 2]);
-                        o.w = __uint_as_float(v[4 * x + 3]);
-                        __stcs(reinterpret_cast<float4 *>(crow + cc * TILE + 4 * x), o);
-                    }
-                }
+                if (row_ok && mj * MT_C + cc < n_tiles) store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane);
             }
             tmem_wait_st();
             tc_fence_before();

@@ -24,7 +24,7 @@ constexpr int P_STAGE_BYTES = P_SPS * P_STEP_BYTES;             // 64 KiB
 constexpr int P_STAGES = 3;
 constexpr int P_THREADS = 192;
 constexpr int P_CTRL_BYTES = 256;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_CTRL_BYTES + 128;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_CTRL_BYTES + 4 * EPI_WARP_BYTES + 128;
 constexpr uint32_t P_TMEM_COLS = 512;
 constexpr uint32_t P_ACC_COLS = MT_C * TILE;                    // 256
 
@@ -287,6 +287,7 @@ gated_multiply_pair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__
     } else {
         // ------------------------------------------------------------------ epilogue (4 warps per block)
         const uint32_t q = (uint32_t)(warp & 3);
+        uint8_t *epi_tile = smem + P_STAGES * P_STAGE_BYTES + P_CTRL_BYTES + (warp - 2) * EPI_WARP_BYTES;
         uint32_t acc_iter = 0;
         unsigned int done = 0;
         bool ok = true;
@@ -302,7 +303,8 @@ gated_multiply_pair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__
             tc_fence_after();
             const int row = mi * (MT_R * TILE) + (int)q * TILE + lane;
             const bool row_ok = row < rows_total;
-            float *crow = c + (int64_t)row * ldc + (int64_t)mj * (MT_C * TILE);
+            // first row of this warp's 32-row block of C, first column of the macro tile
+            float *cblock = c + (int64_t)(row - lane) * ldc + (int64_t)mj * (MT_C * TILE);
 #pragma unroll 1
             for (int cc = 0; cc < MT_C; cc++) {
                 const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * P_ACC_COLS + (uint32_t)cc * TILE;
@@ -310,17 +312,7 @@ gated_multiply_pair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__
                 tmem_ld32(taddr, v);
                 tmem_wait_ld();
                 tmem_st32_zero(taddr);
-                if (row_ok && mj * MT_C + cc < n_tiles) {
-#pragma unroll
-                    for (int x = 0; x < 8; x++) {
-                        float4 o;
-                        o.x = __uint_as_float(v[4 * x + 0]);
-                        o.y = __uint_as_float(v[4 * x + 1]);
-                        o.z = __uint_as_float(v[4 * x + 2]);
-                        o.w = __uint_as_float(v[4 * x + 3]);
-                        __stcs(reinterpret_cast<float4 *>(crow + cc * TILE + 4 * x), o);
-                    }
-                }
+                if (row_ok && mj * MT_C + cc < n_tiles) store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane);
             }
             tmem_wait_st();
             tc_fence_before();

@@ -122,4 +122,28 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 
+// Epilogue store of one 32 x 32 block of C.  tcgen05.ld leaves every thread with the 32 values of ONE row; storing
+// them directly makes each warp instruction touch 32 different lines.  Going through a per-warp shared-memory tile
+// (rows 144 bytes apart: conflict-free for 128-bit accesses both ways) lets every store instruction write four
+// complete 128-byte rows.
+constexpr int EPI_ROW_BYTES = 144;
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;          // 4608 bytes per epilogue warp
+
+__device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const uint32_t *v, float *c_block,
+                                                      int64_t ldc, int lane)
+{
+    uint4 *mine = reinterpret_cast<uint4 *>(warp_tile + lane * EPI_ROW_BYTES);
+#pragma unroll
+    for (int x = 0; x < 8; x++) mine[x] = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+    __syncwarp();
+    const int sub = lane >> 3, part = lane & 7;               // four rows per instruction, eight lanes per row
+#pragma unroll
+    for (int r0 = 0; r0 < 32; r0 += 4) {
+        const int r = r0 + sub;
+        const float4 o = *reinterpret_cast<const float4 *>(warp_tile + r * EPI_ROW_BYTES + part * 16);
+        __stcs(reinterpret_cast<float4 *>(c_block + (int64_t)r * ldc + part * 4), o);
+    }
+    __syncwarp();
+}
+
 }  // namespace spamm
