@@ -50,6 +50,10 @@ constexpr unsigned long long PEER_WAIT_LIMIT_NS = 2000000000ull;
 int peer_wait_selftest_launch(const PeerWait &w, cudaStream_t stream);
 int norm_map_push_launch(const float *d_x, int rows, int cols, int64_t ld, int64_t map_offset, const PeerTargets &t,
                          int rank, unsigned int epoch, cudaStream_t stream);
+// Both norm maps AND the half conversion of every tile of A and B in one launch (for mostly surviving workloads).
+int norm_pack_pair_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a, void *d_half_a,
+                          const float *d_xb, int rows_b, int cols_b, int64_t ldb, float *d_map_b, void *d_half_b,
+                          cudaStream_t stream);
 
 // Internal launchers behind the extern "C" entry points, with the extras the plan uses to save launches:
 //  - the list builder's first kernel can clear a region (counters + need flags) before the lists are built,

@@ -81,6 +81,136 @@ norm_map_pair_kernel(const float *__restrict__ xa, int tile_rows_a, int tile_col
                    (int64_t)(blockIdx.x - blocks_a) * 8 + (threadIdx.x >> 5));
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Norm map and half conversion of EVERY tile in one pass (for workloads where most tiles survive the threshold: the
+// separate conversion kernel would read most of the matrices a second time).  The sums are formed exactly as in
+// norm_strip_value, so the maps are the same bits; while a batch of 8 rows is in registers it is also rounded to
+// half and stored in the packed tile layout (see pack_half.cu).
+//   A (element (row, kk) of a tile at (row/8)*512 + (kk/8)*128 + (row%8)*16 + (kk%8)*2): a lane owns 4 consecutive kk
+//   of every row = 8 bytes; neighbouring lanes swap halves of two rows so that each stores 16 bytes and every pair
+//   of lanes fills a 32-byte sector.
+//   B (stored transposed: element (col, kk=row)): the 8 rows of a batch are the 8 kk of one 16-byte unit for each
+//   of the lane's 4 columns, and those 4 units are adjacent: 64 contiguous bytes per lane and batch.
+__device__ __forceinline__ unsigned int half2_bits(float a, float b)
+{
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<unsigned int *>(&h);
+}
+
+template <bool IS_B>
+__device__ __forceinline__ void norm_pack_strip(const float *__restrict__ x, int tile_rows, int tile_cols, int64_t ld,
+                                                float *__restrict__ map, int64_t strip, uint8_t *__restrict__ half,
+                                                int slabs_per_row)
+{
+    const int lane = threadIdx.x & 31;
+    const int strips_per_row = (tile_cols + 3) >> 2;
+    if (strip >= (int64_t)tile_rows * strips_per_row) return;
+    const int tr = (int)(strip / strips_per_row);
+    const int ts = (int)(strip % strips_per_row);
+    const int col = ts * 128 + lane * 4;
+    const bool in_range = col < tile_cols * TILE;
+    const float *p = x + (int64_t)tr * TILE * ld + col;
+    const int tc = ts * 4 + (lane >> 3);       // tile column of this lane
+    const int g = lane & 7;
+    // start of this lane's packed tile
+    uint8_t *dst;
+    if (IS_B)   // slabs [k = tr][column group], 8 tiles each
+        dst = half + ((int64_t)tr * slabs_per_row + (tc >> 3)) * B_SLAB_BYTES + (tc & 7) * TILE_BYTES;
+    else        // slabs [row group][k = tc], 4 tiles each
+        dst = half + ((int64_t)(tr >> 2) * slabs_per_row + tc) * A_SLAB_BYTES + (tr & 3) * TILE_BYTES;
+
+    float acc = 0.0f;
+#pragma unroll
+    for (int r0 = 0; r0 < TILE; r0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            v[r] = in_range ? __ldcs(reinterpret_cast<const float4 *>(p + (int64_t)(r0 + r) * ld))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            acc = __fmaf_rn(v[r].x, v[r].x, acc);
+            acc = __fmaf_rn(v[r].y, v[r].y, acc);
+            acc = __fmaf_rn(v[r].z, v[r].z, acc);
+            acc = __fmaf_rn(v[r].w, v[r].w, acc);
+        }
+        if (IS_B) {
+            if (in_range) {
+                uint8_t *d = dst + (g >> 1) * 512 + (r0 >> 3) * 128 + (g & 1) * 64;
+                uint4 u;
+                u = make_uint4(half2_bits(v[0].x, v[1].x), half2_bits(v[2].x, v[3].x), half2_bits(v[4].x, v[5].x),
+                               half2_bits(v[6].x, v[7].x));
+                *reinterpret_cast<uint4 *>(d) = u;
+                u = make_uint4(half2_bits(v[0].y, v[1].y), half2_bits(v[2].y, v[3].y), half2_bits(v[4].y, v[5].y),
+                               half2_bits(v[6].y, v[7].y));
+                *reinterpret_cast<uint4 *>(d + 16) = u;
+                u = make_uint4(half2_bits(v[0].z, v[1].z), half2_bits(v[2].z, v[3].z), half2_bits(v[4].z, v[5].z),
+                               half2_bits(v[6].z, v[7].z));
+                *reinterpret_cast<uint4 *>(d + 32) = u;
+                u = make_uint4(half2_bits(v[0].w, v[1].w), half2_bits(v[2].w, v[3].w), half2_bits(v[4].w, v[5].w),
+                               half2_bits(v[6].w, v[7].w));
+                *reinterpret_cast<uint4 *>(d + 48) = u;
+            }
+        } else {
+            const bool odd = (g & 1) != 0;
+#pragma unroll
+            for (int r = 0; r < 8; r += 2) {
+                // rows r (kept by the even lane) and r+1 (kept by the odd lane): each lane gives away the other row
+                const unsigned int e0 = half2_bits(v[r].x, v[r].y), e1 = half2_bits(v[r].z, v[r].w);
+                const unsigned int o0 = half2_bits(v[r + 1].x, v[r + 1].y), o1 = half2_bits(v[r + 1].z, v[r + 1].w);
+                const unsigned int s0 = __shfl_xor_sync(0xffffffffu, odd ? e0 : o0, 1);
+                const unsigned int s1 = __shfl_xor_sync(0xffffffffu, odd ? e1 : o1, 1);
+                if (in_range) {
+                    const int row = r0 + r + (odd ? 1 : 0);
+                    const uint4 u = odd ? make_uint4(s0, s1, o0, o1) : make_uint4(e0, e1, s0, s1);
+                    *reinterpret_cast<uint4 *>(dst + (row >> 3) * 512 + (g >> 1) * 128 + (row & 7) * 16) = u;
+                }
+            }
+        }
+    }
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+    if (in_range && g == 0) map[(int64_t)tr * tile_cols + tc] = __fsqrt_rn(acc);
+}
+
+__global__ void __launch_bounds__(256)
+norm_pack_pair_kernel(const float *__restrict__ xa, int tile_rows_a, int tile_cols_a, int64_t lda,
+                      float *__restrict__ map_a, uint8_t *__restrict__ half_a, unsigned int blocks_a,
+                      const float *__restrict__ xb, int tile_rows_b, int tile_cols_b, int64_t ldb,
+                      float *__restrict__ map_b, uint8_t *__restrict__ half_b)
+{
+    if (blockIdx.x < blocks_a)
+        norm_pack_strip<false>(xa, tile_rows_a, tile_cols_a, lda, map_a, (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5),
+                               half_a, tile_cols_a);
+    else
+        norm_pack_strip<true>(xb, tile_rows_b, tile_cols_b, ldb, map_b,
+                              (int64_t)(blockIdx.x - blocks_a) * 8 + (threadIdx.x >> 5), half_b,
+                              (tile_cols_b + MT_C - 1) / MT_C);
+}
+
+int norm_pack_pair_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a, void *d_half_a,
+                          const float *d_xb, int rows_b, int cols_b, int64_t ldb, float *d_map_b, void *d_half_b,
+                          cudaStream_t stream)
+{
+    if (!d_xa || !d_map_a || !d_xb || !d_map_b || !d_half_a || !d_half_b || rows_a <= 0 || cols_a <= 0 ||
+        rows_b <= 0 || cols_b <= 0 || rows_a % TILE || cols_a % TILE || rows_b % TILE || cols_b % TILE ||
+        lda < cols_a || ldb < cols_b || (lda & 3) || (ldb & 3) || (reinterpret_cast<uintptr_t>(d_xa) & 15) ||
+        (reinterpret_cast<uintptr_t>(d_xb) & 15) || (reinterpret_cast<uintptr_t>(d_half_a) & 15) ||
+        (reinterpret_cast<uintptr_t>(d_half_b) & 15))
+        return SPAMM_ERR_INVALID;
+    const int tra = rows_a / TILE, tca = cols_a / TILE, trb = rows_b / TILE, tcb = cols_b / TILE;
+    const int64_t blocks_a = ((int64_t)tra * ((tca + 3) / 4) + 7) / 8;
+    const int64_t blocks_b = ((int64_t)trb * ((tcb + 3) / 4) + 7) / 8;
+    if (blocks_a + blocks_b > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+    norm_pack_pair_kernel<<<(unsigned)(blocks_a + blocks_b), 256, 0, stream>>>(
+        d_xa, tra, tca, lda, d_map_a, static_cast<uint8_t *>(d_half_a), (unsigned)blocks_a, d_xb, trb, tcb, ldb,
+        d_map_b, static_cast<uint8_t *>(d_half_b));
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}
+
 // All-gather of B's norm-map shares without a collective call: after the norm kernel has written this GPU's share
 // into its own map, one block per destination GPU copies the share into that GPU's map (peer-mapped memory, plain
 // 128-bit stores over NVLink), fences system-wide and raises this GPU's flag there: "share of `rank` for step

@@ -66,6 +66,9 @@ struct spamm_plan {
     int active_scalars = 1;
     bool queues_clean = false;
     int dense_hint = -1;                // last counters read: were at least half of the macro tiles dense (-1: unknown)
+    int pack_mode = SPAMM_PACK_AUTO;    // which tiles are converted to half, see spamm_plan_set_pack_mode
+    int pack_all_hint = -1;             // last counters read: did the lists name at least half of all tiles (-1: unknown)
+    bool packed_all = false;            // the last spamm_norms converted every tile: spamm_pack has nothing to do
     // peer exchange of B's norm-map shares (one process per GPU, see spamm_peer_attach)
     float *d_norm_b_buf[2] = {nullptr, nullptr};   // B's map, double buffered by step parity; d_norm_b is the current
     unsigned int *d_peer_flags = nullptr;          // [MAX_PEERS] arrival flags + [1] block counter of the push kernel
@@ -141,6 +144,14 @@ int read_scalars(spamm_plan *p)
     unsigned long long dense = 0;
     for (int c = 0; c < p->active_scalars; c++) dense += p->h_scalars[c].dense_count;
     p->dense_hint = (dense * 2 >= p->n_mt() && p->n_mt() > 0) ? 1 : 0;
+    // and whether they named most of the operand tiles: the next spamm_norms then converts all tiles while it has
+    // them in registers instead of leaving the named ones to a second pass over the matrices
+    if (p->have_lists && p->active_scalars == 1) {
+        const unsigned long long named = p->h_scalars[0].tile_count - p->h_scalars[0].tile_begin;
+        const unsigned long long all = (unsigned long long)p->row_tiles * p->k_tiles +
+                                       (unsigned long long)p->k_tiles * p->n_tiles;
+        p->pack_all_hint = (all > 0 && named * 2 >= all) ? 1 : 0;
+    }
     return SPAMM_OK;
 }
 
@@ -185,6 +196,13 @@ static int setup_chunk_orders(spamm_plan *p)
 }
 
 extern "C" {
+
+int spamm_plan_set_pack_mode(spamm_plan *p, int mode)
+{
+    if (!p || (mode != SPAMM_PACK_AUTO && mode != SPAMM_PACK_LISTED && mode != SPAMM_PACK_ALL)) return SPAMM_ERR_INVALID;
+    p->pack_mode = mode;
+    return SPAMM_OK;
+}
 
 int spamm_plan_set_chunk_tiles(spamm_plan *p, int tiles)
 {
@@ -349,6 +367,7 @@ int spamm_norm_b_share(spamm_plan *p, int b_tile_begin, int b_tile_count)
         p->launches++;
     }
     p->have_lists = p->have_pack = false;
+    p->packed_all = false;
     return SPAMM_OK;
 }
 
@@ -363,6 +382,7 @@ int spamm_norm_a(spamm_plan *p)
     }
     p->have_norms = true;       // the caller answers for B's map (spamm_norm_b_share + its exchange)
     p->have_lists = p->have_pack = false;
+    p->packed_all = false;
     return SPAMM_OK;
 }
 
@@ -449,6 +469,7 @@ int spamm_norm_b_share_push(spamm_plan *p, int b_tile_begin, int b_tile_count)
     p->launches += 2;
     p->peer_wait_pending = true;
     p->have_lists = p->have_pack = false;
+    p->packed_all = false;
     return SPAMM_OK;
 }
 
@@ -457,10 +478,14 @@ int spamm_norms(spamm_plan *p)
     if (!p) return SPAMM_ERR_INVALID;
     if (p->row_tiles == 0) return spamm_norms_share(p, 0, p->k_tiles);
     DeviceGuard guard(p->device);
-    // both maps in one launch
-    int st = spamm_norm_map_pair_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->d_b, p->K, p->N, p->N,
-                                     p->d_norm_b, p->stream);
+    // both maps in one launch; with the conversion of every tile to half when most tiles are going to be needed
+    const bool all = p->pack_mode == SPAMM_PACK_ALL || (p->pack_mode == SPAMM_PACK_AUTO && p->pack_all_hint == 1);
+    int st = all ? norm_pack_pair_launch(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->d_half_a, p->d_b,
+                                         p->K, p->N, p->N, p->d_norm_b, p->d_half_b, p->stream)
+                 : spamm_norm_map_pair_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->d_b, p->K, p->N,
+                                           p->N, p->d_norm_b, p->stream);
     if (st) return st;
+    p->packed_all = all;
     p->launches++;
     p->have_norms = true;
     p->have_lists = p->have_pack = false;
@@ -491,6 +516,7 @@ int spamm_build_lists(spamm_plan *p, float tau)
         p->peer_wait_pending = false;
         if (st) return st;
         p->launches += 2;
+        p->queues_clean = true;     // the clear covers the multiply's two work counters
     } else {
         SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
     }
@@ -504,7 +530,7 @@ int spamm_pack(spamm_plan *p)
     if (!p) return SPAMM_ERR_INVALID;
     if (!p->have_lists) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
-    if (p->row_tiles) {
+    if (p->row_tiles && !p->packed_all) {
         int st = pack_half_launch(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->d_tile_list, p->scalars(),
                                   p->d_half_a, p->d_half_b, true, p->stream);
         if (st) return st;
@@ -567,6 +593,10 @@ static void fill_stats(spamm_plan *p, spamm_stats *s)
     for (int c = 0; c < p->active_scalars; c++) {
         s->packed_tiles_a += (int64_t)p->h_scalars[c].packed_a;
         s->packed_tiles_b += (int64_t)p->h_scalars[c].packed_b;
+    }
+    if (p->packed_all) {            // converted by the norm pass: every tile, listed or not
+        s->packed_tiles_a = (int64_t)p->row_tiles * p->k_tiles;
+        s->packed_tiles_b = (int64_t)p->k_tiles * p->n_tiles;
     }
     s->executed_flops = 65536.0 * (double)s->survivors;
 }
@@ -696,6 +726,7 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
     // Large problem: the copies dominate (PCIe), so they are overlapped with each other and with the kernels.
     // B goes up first (every C row needs all of it); then the rows of A go up chunk by chunk, each chunk runs the
     // whole path on the main stream, and its rows of C go down on a second stream while the next chunk goes up.
+    p->packed_all = false;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
     SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
     SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream));

@@ -132,6 +132,14 @@ class SpammPlan:
         """Tile rows per chunk of the pipelined `multiply` (multiple of 4)."""
         check(self._lib.spamm_plan_set_chunk_tiles(self._h, int(tiles)), "spamm_plan_set_chunk_tiles")
 
+    def set_pack_mode(self, mode: str) -> None:
+        """Which tiles are converted to half: "auto" (default), "listed" (only tiles a skip list names, by `pack`)
+        or "all" (every tile, inside `norms`).  Results are the same in every mode."""
+        modes = {"auto": 0, "listed": 1, "all": 2}
+        if mode not in modes:
+            raise ValueError(f"pack mode must be one of {sorted(modes)}")
+        check(self._lib.spamm_plan_set_pack_mode(self._h, modes[mode]), "spamm_plan_set_pack_mode")
+
     # ---- the driver steps
     def upload(self, a_rows=None, b=None) -> None:
         pa = _host_ptr(a_rows, self.rows * self.K * 4) if a_rows is not None else 0

@@ -188,6 +188,19 @@ int spamm_multiply(spamm_plan *plan, const float *a_rows, const float *b, float 
  */
 int spamm_plan_set_chunk_tiles(spamm_plan *plan, int tiles);
 
+/*
+ * Which tiles spamm_norms / spamm_pack convert to half.  The reference converts whole matrices on the host when it
+ * generates them (tool.cu:418); here the conversion runs on the GPU inside the timed step:
+ *   SPAMM_PACK_LISTED  only the tiles some skip list names, by spamm_pack (best when few products survive);
+ *   SPAMM_PACK_ALL     every tile, by spamm_norms while it has the tile in registers (best when most survive:
+ *                      the matrices are read once instead of twice); spamm_pack then launches nothing;
+ *   SPAMM_PACK_AUTO    (default) LISTED, until counters read back by spamm_sync / spamm_run_timed show that the
+ *                      lists named at least half of all tiles; then ALL, until they show otherwise.
+ * Results are identical in every mode.
+ */
+enum { SPAMM_PACK_AUTO = 0, SPAMM_PACK_LISTED = 1, SPAMM_PACK_ALL = 2 };
+int spamm_plan_set_pack_mode(spamm_plan *plan, int mode);
+
 /* Same as spamm_run but records per-phase events; blocking.  Inputs must already be resident. */
 int spamm_run_timed(spamm_plan *plan, float tau, spamm_stats *stats);
 

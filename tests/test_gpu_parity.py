@@ -198,3 +198,59 @@ def test_dense_macro_tiles_with_and_without_the_paired_kernel(oracle):
             p.sync()
             assert p.counts()[1] == S2
             assert rel_fro(p.download_c(), C_ref2) <= C_TOL
+
+
+def test_half_conversion_modes_give_the_same_result(oracle):
+    """Tiles are converted to half either one by one as the lists name them (its own kernel) or all of them inside
+    the norm pass; "auto" switches on counters read back from the previous step.  The mode is a speed choice: maps,
+    lists and C must not depend on it."""
+    from cuspamm_b200 import SpammPlan
+
+    rng = np.random.default_rng(17)
+    # shapes that leave partial macro tiles (5 tile rows, 11 tile columns) and partial strips (7 tiles of K)
+    M, K, N = 160, 224, 352
+    A = (rng.standard_normal((M, K)) * np.exp(-rng.random((M, K)) * 5)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * np.exp(-rng.random((K, N)) * 5)).astype(np.float32)
+    nA, nB = oracle.norm_map(A), oracle.norm_map(B)
+    for tau in (0.0, float(np.median(nA[:, :, None] * nB[None])), 1e9):
+        C_ref, S = oracle.spamm(A, B, tau)
+        out = {}
+        for mode in ("listed", "all"):
+            with SpammPlan(M, K, N) as p:
+                p.set_pack_mode(mode)
+                p.upload(A, B)
+                st = p.run_timed(tau)
+                assert st["survivors"] == S
+                if mode == "all":
+                    assert st["packed_tiles_a"] == nA.size and st["packed_tiles_b"] == nB.size
+                assert np.array_equal(p.norm_a().view(np.uint32), nA.view(np.uint32))
+                assert np.array_equal(p.norm_b().view(np.uint32), nB.view(np.uint32))
+                out[mode] = p.download_c()
+            assert rel_fro(out[mode], C_ref) <= C_TOL
+        assert np.array_equal(out["listed"], out["all"]), "C depends on the conversion mode"
+
+    # auto: dense lists turn the conversion-in-the-norm-pass on for the next step, sparse lists turn it off again
+    n = 512
+    A = signed_decay(n, 0.002, seed=71)
+    B = signed_decay(n, 0.002, seed=72)
+    C_dense, S_dense = oracle.spamm(A, B, 0.0)
+    tau_mid = 0.4
+    C_mid, S_mid = oracle.spamm(A, B, tau_mid)
+    all_tiles = (n // 32) ** 2
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        seen = []
+        for tau, C_ref, S in ((0.0, C_dense, S_dense), (0.0, C_dense, S_dense), (tau_mid, C_mid, S_mid),
+                              (1e12, None, 0), (1e12, None, 0), (0.0, C_dense, S_dense)):
+            st = p.run_timed(tau)
+            assert st["survivors"] == S
+            C = p.download_c()
+            if C_ref is None:
+                assert not C.any()
+            else:
+                assert rel_fro(C, C_ref) <= C_TOL
+            seen.append(st["packed_tiles_a"])
+    # step 1 converts what the lists name (= everything at tau=0), step 2 and 3 everything in the norm pass,
+    # step 4 still everything (the hint comes from step 3 only if that named most tiles), step 5 nothing
+    assert seen[0] == all_tiles and seen[1] == all_tiles
+    assert seen[4] == 0
