@@ -57,7 +57,8 @@ int norm_pack_pair_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda
 
 // Internal launchers behind the extern "C" entry points, with the extras the plan uses to save launches:
 //  - the list builder's first kernel can clear a region (counters + need flags) before the lists are built,
-//  - the packing kernel can reset the multiply's two work counters, which the multiply launcher then leaves alone.
+//  - the packing kernel can reset the multiply's two work counters, which the multiply launcher then leaves alone,
+//  - the multiply can be told that C was cleared beforehand: it then writes only macro tiles that have steps.
 int build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles, float tau,
                        void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
                        uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list, int32_t *d_busy_list,
@@ -69,7 +70,7 @@ int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_ti
 int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                           const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                           spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                          int64_t ldc, bool reset_queues, bool try_pairs, cudaStream_t stream);
+                          int64_t ldc, bool reset_queues, bool try_pairs, bool c_zeroed, cudaStream_t stream);
 
 int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const int32_t *d_step_counts,
                                spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,

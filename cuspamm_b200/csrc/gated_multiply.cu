@@ -91,7 +91,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                       const uint32_t *__restrict__ steps, const int32_t *__restrict__ step_counts,
                       const int32_t *__restrict__ order, const int32_t *__restrict__ busy_list,
                       spamm_list_scalars *__restrict__ sc, int row_tiles, int k_tiles, int n_tiles,
-                      float *__restrict__ c, int64_t ldc, int pairs_launched)
+                      float *__restrict__ c, int64_t ldc, int pairs_launched, int c_zeroed)
 {
     extern __shared__ uint8_t smem_raw[];
     // stage data first (128-byte aligned), control block after it
@@ -187,7 +187,9 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 if (pair_owned(mt, cnt)) continue;
                 cnt = step_count_of(cnt);
             } else {
-                bool exhausted = false;
+                // with C cleared beforehand only macro tiles that have steps are written: none are left in this phase
+                // when the first phase has handled them
+                bool exhausted = c_zeroed && use_busy;
                 while (!pending && !exhausted) {
                     unsigned int p0 = 0;
                     if (lane == 0) p0 = atomicAdd(&sc->queue_all, chunk);
@@ -202,6 +204,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                         const int raw = step_counts[cand_mt];
                         cand_cnt = step_count_of(raw);
                         if (use_busy && cand_cnt > 0) cand_mt = -1;     // already handled in the first phase
+                        else if (c_zeroed && cand_cnt == 0) cand_mt = -1;   // already zero
                         else if (pair_owned(cand_mt, raw)) cand_mt = -1;
                     }
                     pending = __ballot_sync(0xffffffffu, cand_mt >= 0);
@@ -418,7 +421,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         // group of 64 threads that claims four macro tiles at a time from the same counter the scheduler uses for
         // its second phase; the next claim is issued before the current tiles are written.
         const unsigned int busy_n = sc->busy_count;
-        if (busy_n * 4u <= n_mt && !nothing_left) {
+        if (busy_n * 4u <= n_mt && !nothing_left && !c_zeroed) {
             const int pair_lane = threadIdx.x & 63;          // index inside the group of two warps
             const uint32_t bar_id = 1u + (uint32_t)((warp - 6) >> 1);
             volatile int32_t *claim = &ctrl->filler_claim[(warp - 6) >> 1][0];
@@ -517,13 +520,13 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
                                         int k_tiles, int n_tiles, float *d_c, int64_t ldc, void *stream)
 {
     return spamm::gated_multiply_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_order, d_busy_list, d_scalars,
-                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, true, (cudaStream_t)stream);
+                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, true, false, (cudaStream_t)stream);
 }
 
 int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                                  const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                                  spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                                 int64_t ldc, bool reset_queues, bool try_pairs, cudaStream_t stream)
+                                 int64_t ldc, bool reset_queues, bool try_pairs, bool c_zeroed, cudaStream_t stream)
 {
     using namespace spamm;
     if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
@@ -562,7 +565,7 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
     gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, stream>>>(
         static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
-        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, try_pairs ? 1 : 0);
+        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, try_pairs ? 1 : 0, c_zeroed ? 1 : 0);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -59,6 +59,9 @@ struct spamm_plan {
     cudaEvent_t ev[8] = {};
     cudaStream_t stream_d2h = nullptr;  // second stream: copies C chunks out while the next chunk is computed
     cudaEvent_t ev_chunk[MAX_CHUNKS] = {};
+    cudaEvent_t ev_zero[2] = {};        // fork / join of the early clearing of C on the second stream
+    int zero_hint = -1;                 // last counters read: did at most a quarter of the macro tiles have steps
+    bool c_zero_pending = false;        // C is being cleared on the second stream; the multiply writes busy tiles only
     int chunk_tiles = 0;                // tile rows per chunk of the pipelined spamm_multiply (multiple of 4)
     int n_chunks = 1;
     int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
@@ -144,6 +147,11 @@ int read_scalars(spamm_plan *p)
     unsigned long long dense = 0;
     for (int c = 0; c < p->active_scalars; c++) dense += p->h_scalars[c].dense_count;
     p->dense_hint = (dense * 2 >= p->n_mt() && p->n_mt() > 0) ? 1 : 0;
+    // and whether few macro tiles had steps: the next step then clears C with a memset on the second stream while
+    // the lists are built and the tiles converted (kernels that leave the memory system idle), and its multiply
+    // writes only the macro tiles that have steps
+    if (p->have_lists && p->active_scalars == 1)
+        p->zero_hint = ((unsigned long long)p->h_scalars[0].busy_count * 4ull <= p->n_mt()) ? 1 : 0;
     // and whether they named most of the operand tiles: the next spamm_norms then converts all tiles while it has
     // them in registers instead of leaving the named ones to a second pass over the matrices
     if (p->have_lists && p->active_scalars == 1) {
@@ -173,6 +181,10 @@ int64_t total_survivors(const spamm_plan *p)
 }
 
 }  // namespace
+
+extern "C" {
+static int build_lists_impl(spamm_plan *p, float tau, bool whole_step);
+}
 
 // (Re)builds the macro-tile orders for the chunk shapes of the pipelined spamm_multiply.
 static int setup_chunk_orders(spamm_plan *p)
@@ -245,10 +257,20 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
         spamm_plan_destroy(p);
         return code;
     };
-    if (cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaStreamCreateWithFlags(&p->stream_d2h, cudaStreamNonBlocking) != cudaSuccess)
-        return fail(record_cuda_error(cudaGetLastError(), "cudaStreamCreate"));
+    {
+        // The main stream gets a priority above the second one: when C is cleared on the second stream beside the
+        // list build, the blocks of the (small) list kernels must not queue behind those of the memset.
+        int least = 0, greatest = 0;
+        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) least = greatest = 0;
+        const int main_priority = greatest < least ? least - 1 : least;
+        if (cudaStreamCreateWithPriority(&p->stream, cudaStreamNonBlocking, main_priority) != cudaSuccess ||
+            cudaStreamCreateWithPriority(&p->stream_d2h, cudaStreamNonBlocking, least) != cudaSuccess)
+            return fail(record_cuda_error(cudaGetLastError(), "cudaStreamCreate"));
+    }
     for (auto &e : p->ev_chunk)
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
+            return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
+    for (auto &e : p->ev_zero)
         if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
             return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
     {
@@ -336,6 +358,8 @@ int spamm_plan_destroy(spamm_plan *p)
     for (auto &e : p->ev)
         if (e) cudaEventDestroy(e);
     for (auto &e : p->ev_chunk)
+        if (e) cudaEventDestroy(e);
+    for (auto &e : p->ev_zero)
         if (e) cudaEventDestroy(e);
     cudaFree(p->d_order_chunk); cudaFree(p->d_order_last);
     if (p->stream_d2h) cudaStreamDestroy(p->stream_d2h);
@@ -495,18 +519,43 @@ int spamm_norms(spamm_plan *p)
 int spamm_finish(spamm_plan *p, float tau)
 {
     int st;
-    if ((st = spamm_build_lists(p, tau))) return st;
+    if ((st = build_lists_impl(p, tau, true))) return st;
     if ((st = spamm_pack(p))) return st;
     return spamm_gated_multiply(p);
 }
 
+int spamm_clear_c_early(spamm_plan *p)
+{
+    if (!p) return SPAMM_ERR_INVALID;
+    if (!p->row_tiles || p->zero_hint != 1 || p->c_zero_pending) return SPAMM_OK;
+    DeviceGuard guard(p->device);
+    // few macro tiles are expected to have steps: clear all of C now, on the second stream, beside whatever the
+    // main stream does until the multiply (exchange of norm maps, list build, conversion)
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev_zero[0], p->stream));
+    SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_d2h, p->ev_zero[0], 0));
+    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_c, 0, p->bytes_c(), p->stream_d2h));
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev_zero[1], p->stream_d2h));
+    p->c_zero_pending = true;
+    return SPAMM_OK;
+}
+
 int spamm_build_lists(spamm_plan *p, float tau)
+{
+    return build_lists_impl(p, tau, false);       // on its own it leaves C alone
+}
+
+// `whole_step`: the packing and the multiply follow at once, so C may be cleared early (see zero_hint).
+static int build_lists_impl(spamm_plan *p, float tau, bool whole_step)
 {
     if (!p) return SPAMM_ERR_INVALID;
     if (!p->have_norms) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     p->active_scalars = 1;
     PeerWait wait{p->d_peer_flags, p->peer_world, p->peer_epoch, p->d_peer_error, PEER_WAIT_LIMIT_NS};
+    if (whole_step) {
+        int st = spamm_clear_c_early(p);
+        if (st) return st;
+    }
     if (p->row_tiles) {
         // the builder's first kernel clears the counters and need flags: no separate memset on the stream
         int st = build_lists_launch(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
@@ -547,9 +596,12 @@ int spamm_gated_multiply(spamm_plan *p)
     if (!p->have_pack) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     if (p->row_tiles) {
+        const bool zeroed = p->c_zero_pending;
+        if (zeroed) SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_zero[1], 0));
+        p->c_zero_pending = false;      // consumed: a second multiply on the same lists writes all of C itself
         int st = gated_multiply_launch(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
                                        p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N,
-                                       !p->queues_clean, p->dense_hint != 0, p->stream);
+                                       !p->queues_clean, p->dense_hint != 0, zeroed, p->stream);
         p->queues_clean = false;
         if (st) return st;
         p->launches++;
@@ -561,7 +613,7 @@ int spamm_run(spamm_plan *p, float tau)
 {
     int st;
     if ((st = spamm_norms(p))) return st;
-    if ((st = spamm_build_lists(p, tau))) return st;
+    if ((st = build_lists_impl(p, tau, true))) return st;
     if ((st = spamm_pack(p))) return st;
     return spamm_gated_multiply(p);
 }
@@ -625,7 +677,7 @@ static int run_with_events(spamm_plan *p, float tau)
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[0], p->stream));
     if ((st = spamm_norms(p))) return st;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[1], p->stream));
-    if ((st = spamm_build_lists(p, tau))) return st;
+    if ((st = build_lists_impl(p, tau, true))) return st;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[2], p->stream));
     if ((st = spamm_pack(p))) return st;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[3], p->stream));
@@ -691,7 +743,7 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
         return st;
     if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->dense_hint != 0, stream)))
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->dense_hint != 0, false, stream)))
         return st;
     p->launches += do_norm ? 5 : 4;
     return SPAMM_OK;

@@ -181,6 +181,10 @@ class SpammPlan:
     def run(self, tau: float) -> None:
         check(self._lib.spamm_run(self._h, float(tau)), "spamm_run")
 
+    def clear_c_early(self) -> None:
+        """Announce that lists, pack and multiply follow: C may be cleared now on the second stream (a speed hint)."""
+        check(self._lib.spamm_clear_c_early(self._h), "spamm_clear_c_early")
+
     def finish(self, tau: float) -> None:
         """lists + pack + multiply in one call."""
         check(self._lib.spamm_finish(self._h, float(tau)), "spamm_finish")
@@ -366,6 +370,7 @@ class ShardedSpamm:
             # this rank's share of B's map goes straight into every GPU's map from inside the norm kernel
             self.plan.norm_b_share_push(self.rank * self._share, self._share)
             self.plan.compute_norm_a()
+            self._clear_c_early()
         else:
             if self._nb is None:      # views and streams are built once: this runs every step
                 self._nb = self.plan.as_tensor(BUF_NORM_B)
@@ -382,6 +387,7 @@ class ShardedSpamm:
                 with self._torch.cuda.stream(self._side):
                     self._dist.all_gather_into_tensor(nb, mine, group=self.group)   # in place
                 self.plan.compute_norm_a()
+                self._clear_c_early()          # beside the exchange, not after it
                 self._stream.wait_stream(self._side)
             else:
                 self.plan.norms_share(self.rank * self._share, self._share)
@@ -394,6 +400,11 @@ class ShardedSpamm:
             self.plan.build_lists(tau)
             self.plan.pack()
             self.plan.gated_multiply()
+
+    def _clear_c_early(self) -> None:
+        f = getattr(self.plan, "clear_c_early", None)
+        if f is not None:
+            f()
 
     def run_timed(self, tau: float) -> dict:
         """One `run` with CUDA events between its parts (this rank's view, milliseconds); blocking."""

@@ -189,6 +189,16 @@ int spamm_multiply(spamm_plan *plan, const float *a_rows, const float *b, float 
 int spamm_plan_set_chunk_tiles(spamm_plan *plan, int tiles);
 
 /*
+ * Optional, for callers that issue the steps one by one (spamm_run and spamm_finish do this themselves): announces
+ * that the rest of a whole step (lists, pack, multiply) follows.  If the counters read back by the last spamm_sync /
+ * spamm_run_timed showed that at most a quarter of the 128 x 256 blocks of C received any product, all of C is
+ * cleared now with a memset on the plan's second stream, beside the work of the main stream, and the next
+ * spamm_gated_multiply writes only the blocks that receive products; otherwise nothing happens.  The result is
+ * the same either way.  The reference writes every C tile from its multiply kernel (cuSpAMM.cu:381-390).
+ */
+int spamm_clear_c_early(spamm_plan *plan);
+
+/*
  * Which tiles spamm_norms / spamm_pack convert to half.  The reference converts whole matrices on the host when it
  * generates them (tool.cu:418); here the conversion runs on the GPU inside the timed step:
  *   SPAMM_PACK_LISTED  only the tiles some skip list names, by spamm_pack (best when few products survive);

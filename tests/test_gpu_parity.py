@@ -254,3 +254,39 @@ def test_half_conversion_modes_give_the_same_result(oracle):
     # step 4 still everything (the hint comes from step 3 only if that named most tiles), step 5 nothing
     assert seen[0] == all_tiles and seen[1] == all_tiles
     assert seen[4] == 0
+
+
+def test_c_cleared_early_when_few_macro_tiles_have_steps(oracle):
+    """When the counters of the previous step show that few macro tiles have steps, the next step clears C with a
+    memset beside the list build and its multiply writes only the macro tiles that have steps.  Whatever C held
+    before and whatever the hint said, the result must be the checker's, with exact zeros in the empty tiles."""
+    from cuspamm_b200 import SpammPlan
+
+    n = 2048
+    A = signed_decay(n, 0.5, seed=81)             # narrow band: about a fifth of the macro tiles have steps
+    B = signed_decay(n, 0.5, seed=82)
+    refs = {tau: oracle.spamm(A, B, tau, want_maps=True) for tau in (1e-6, 0.0)}
+    busy = (refs[1e-6][4].reshape(n // 128, 4, n // 256, 8) > 0).any(axis=(1, 3))
+    assert 0 < busy.mean() <= 0.25, "the workload does not reach the early-clearing path"
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        for tau in (0.0, 1e-6, 1e-6, 1e-6, 0.0, 0.0, 1e-6):
+            p.run(tau)
+            p.sync()                              # reading the counters refreshes the hint
+            C = p.download_c()
+            C_ref, S, _, _, counts = refs[tau]
+            assert p.counts()[1] == S
+            assert rel_fro(C, C_ref) <= C_TOL
+            Ct = C.reshape(n // 32, 32, n // 32, 32).transpose(0, 2, 1, 3)
+            assert not Ct[counts == 0].any(), "an empty tile is not zero"
+        # the lists alone leave C alone, and a multiply repeated on the same lists writes all of C again
+        p.run(1e-6)
+        p.sync()
+        C1 = p.download_c()
+        p.build_lists(1e-6)
+        assert np.array_equal(p.download_c(), C1)
+        p.pack()
+        p.gated_multiply()
+        p.gated_multiply()
+        p.sync()
+        assert np.array_equal(p.download_c(), C1)
