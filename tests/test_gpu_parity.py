@@ -290,3 +290,26 @@ def test_c_cleared_early_when_few_macro_tiles_have_steps(oracle):
         p.gated_multiply()
         p.sync()
         assert np.array_equal(p.download_c(), C1)
+
+
+def test_c_cleared_early_with_cut_macro_tiles(oracle):
+    """The same path where the last macro-tile row and column of C are cut (93 x 95 tiles) and have products."""
+    from cuspamm_b200 import SpammPlan
+
+    M, K, N = 2976, 3104, 3040
+    A = np.ascontiguousarray(signed_decay(3104, 0.5, seed=83)[:M, :K])
+    B = np.ascontiguousarray(signed_decay(3104, 0.5, seed=84)[:K, :N])
+    C_ref, S, _, _, counts = oracle.spamm(A, B, 1e-6, want_maps=True)
+    pad = np.zeros((96, 96), dtype=bool)
+    pad[:93, :95] = counts > 0
+    busy = pad.reshape(24, 4, 12, 8).any(axis=(1, 3))
+    assert busy[-1].any() and busy[:, -1].any() and busy.mean() <= 0.25
+    with SpammPlan(M, K, N) as p:
+        p.upload(A, B)
+        for _ in range(3):
+            p.run(1e-6)
+            p.sync()
+            C = p.download_c()
+            assert p.counts()[1] == S
+            assert rel_fro(C, C_ref) <= C_TOL
+            assert not C.reshape(93, 32, 95, 32).transpose(0, 2, 1, 3)[counts == 0].any()
