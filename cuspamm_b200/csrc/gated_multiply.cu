@@ -335,7 +335,9 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ tensor-core issue
-        if (lane == 0) {
+        // Every lane runs the loop (waits, addresses, descriptors are then the same in all lanes of the warp, which
+        // measurably shortens the issue path); lane 0 alone issues the multiplies, commits and arrives.
+        {
             uint32_t slot = 0, acc_iter = 0;
             bool ok = true;
             // descriptor without the start address: adding (address >> 4) completes it, +16 is the second K=16 half
@@ -348,7 +350,8 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 if (!ok) break;
                 const int mt = ctrl->tile_slot[d];
                 const int cnt = ctrl->tile_cnt[d];
-                mbar_arrive(smem_u32(&ctrl->sched_empty[d]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[d]));
                 if (mt < 0) break;
                 if (cnt == 0) continue;
                 const uint32_t buf = acc_iter & 1u;
@@ -365,6 +368,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                     last = ctrl->stage_last[s] != 0u;
                     const uint32_t a_stage = stage0 + s * STAGE_BYTES;
                     const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+                    if (lane == 0) {
 #pragma unroll
                     for (int t = 0; t < SPS; t++) {
                         const uint32_t a_addr = a_stage + t * A_SLAB_BYTES;
@@ -377,8 +381,8 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                             if ((w >> 16) == 0xfffu) {
                                 // every row and every column of the macro tile: two instructions with N = 256
                                 const uint64_t db = desc0 + (uint64_t)(b_addr >> 4);
-                                umma_f16(dbase, da, db, IDESC_N256, 0u, 0u, 0u, 0u);
-                                umma_f16(dbase, da + 16u, db + 16u, IDESC_N256, 0u, 0u, 0u, 0u);
+                                umma_f16_all_rows(dbase, da, db, IDESC_N256);
+                                umma_f16_all_rows(dbase, da + 16u, db + 16u, IDESC_N256);
                             } else {
                                 const uint32_t rows = step_rows(w), cols = step_cols(w);
                                 const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
@@ -400,13 +404,15 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                         }
                     }
                     umma_commit(smem_u32(&ctrl->empty[s]));
+                    }
+                    __syncwarp();
                     slot++;
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+                if (lane == 0) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
                 acc_iter++;
             }
-            if (*abort_flag) {
+            if (*abort_flag && lane == 0) {
                 // wait for the multiplies already issued before tensor memory is freed
                 umma_commit(smem_u32(&ctrl->drain));
                 const unsigned long long t0 = global_ns();

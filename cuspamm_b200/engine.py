@@ -75,6 +75,57 @@ def row_blocks(row_tiles: int, world: int) -> list:
     return out
 
 
+def balanced_row_blocks(weights, world: int, unit: int = MT_ROWS) -> list:
+    """Contiguous blocks of C tile rows, one per GPU, whose largest total weight is as small as a contiguous split
+    on multiples of `unit` tile rows allows.  `weights[i]` is the cost of tile row i (for example its number of
+    surviving products plus a constant for the row's share of the norm pass and of writing C).  The reference
+    always splits evenly (cuSpAMM.cu:503,530), which leaves GPUs idle when the survivors are unevenly spread
+    (a lattice, a matrix with a dense corner).  Returns [(begin, count)] * world; every block gets at least one
+    unit when there are enough units."""
+    w = np.asarray(weights, dtype=np.float64)
+    row_tiles = int(w.shape[0])
+    if world <= 0 or w.ndim != 1 or (w < 0).any():
+        raise ValueError("bad partition")
+    if not w.any():
+        return row_blocks(row_tiles, world)
+    if row_tiles < unit * world:
+        unit = 1
+    n_units = -(-row_tiles // unit)
+    uw = np.array([w[u * unit:(u + 1) * unit].sum() for u in range(n_units)], dtype=np.float64)
+
+    def cut(cap: float):
+        """Greedy split: a block is closed when the next unit would exceed `cap`, or when the units left are just
+        enough to give every remaining block one.  Returns the unit index where every block starts."""
+        starts, load = [0], 0.0
+        for u in range(n_units):
+            must = n_units - u <= world - len(starts) and u > starts[-1]
+            if u > starts[-1] and (load + uw[u] > cap or must) and len(starts) < world:
+                starts.append(u)
+                load = 0.0
+            load += uw[u]
+        return starts
+
+    def worst(starts):
+        ends = starts[1:] + [n_units]
+        return max(uw[a:b].sum() for a, b in zip(starts, ends)) if n_units else 0.0
+
+    lo, hi = (float(uw.max()) if n_units else 0.0), float(uw.sum())
+    for _ in range(60):                       # bisection on the largest block weight
+        mid = 0.5 * (lo + hi)
+        if worst(cut(mid)) <= mid:
+            hi = mid
+        else:
+            lo = mid
+    starts = cut(hi)
+    starts += [n_units] * (world - len(starts))          # more GPUs than units: empty blocks at the end
+    out = []
+    for r in range(world):
+        b = min(starts[r] * unit, row_tiles)
+        e = min((starts[r + 1] if r + 1 < world else n_units) * unit, row_tiles)
+        out.append((b, e - b))
+    return out
+
+
 class _DeviceView:
     """Zero-copy view of plan-owned device memory for torch.as_tensor."""
 
@@ -313,7 +364,7 @@ class ShardedSpamm:
     """
 
     def __init__(self, M: int, K: int, N: int, group=None, plan_factory=None, device: Optional[int] = None,
-                 exchange: str = "nccl"):
+                 exchange: str = "nccl", blocks=None):
         import torch
         import torch.distributed as dist
 
@@ -322,7 +373,15 @@ class ShardedSpamm:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.M, self.K, self.N = M, K, N
-        self.blocks = row_blocks(M // TILE, self.world)
+        if blocks is None:
+            blocks = row_blocks(M // TILE, self.world)          # the reference's even split
+        else:                                                   # e.g. from balanced_row_blocks
+            blocks = [(int(b), int(c)) for b, c in blocks]
+            ends = [b + c for b, c in blocks]
+            if (len(blocks) != self.world or blocks[0][0] != 0 or ends[-1] != M // TILE
+                    or any(c < 0 for _, c in blocks) or any(blocks[i + 1][0] != ends[i] for i in range(self.world - 1))):
+                raise ValueError("blocks must tile the C tile rows contiguously, one block per rank")
+        self.blocks = blocks
         self.row_tile_begin, self.row_tile_count = self.blocks[self.rank]
         if plan_factory is None:
             dev = torch.cuda.current_device() if device is None else device
@@ -452,6 +511,17 @@ class ShardedSpamm:
         t = self._torch.tensor([s], dtype=self._torch.int64, device=dev)
         self._dist.all_reduce(t, group=self.group)
         return int(t.item())
+
+    def row_survivors(self) -> np.ndarray:
+        """Surviving products per C tile row of the last step, for all tile rows, on every rank (the input of
+        `balanced_row_blocks`)."""
+        counts, _ = self.plan.counts()
+        mine = counts.sum(axis=1).astype(np.int64)
+        if self.world == 1:
+            return mine
+        parts = [None] * self.world
+        self._dist.all_gather_object(parts, mine, group=self.group)
+        return np.concatenate([np.asarray(x, dtype=np.int64) for x in parts])
 
     def gather_c(self, dst: int = 0):
         """Gathers the C slabs on rank `dst` (device to device), returns the full C there as a tensor, else None."""

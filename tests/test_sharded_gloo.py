@@ -113,3 +113,73 @@ def test_two_ranks_reproduce_the_single_rank_result(tmp_path, oracle, world, n):
     C_ref, S_ref = oracle.spamm(A, B, tau)
     assert int(np.load(tmp_path / "S.npy")[0]) == S_ref
     assert np.array_equal(np.load(tmp_path / "C.npy"), C_ref)
+
+
+def test_balanced_row_blocks_properties():
+    """The survivor-balanced split: contiguous, complete, on macro-tile boundaries, never worse than the even split."""
+    from cuspamm_b200 import balanced_row_blocks, row_blocks
+
+    rng = np.random.default_rng(5)
+    for T, world in [(1024, 8), (1024, 4), (512, 2), (100, 3), (64, 8), (7, 4), (3, 8), (0, 2)]:
+        w = rng.random(T) ** 4 * 1000 + 5
+        blocks = balanced_row_blocks(w, world)
+        assert len(blocks) == world and blocks[0][0] == 0 and sum(c for _, c in blocks) == T
+        assert all(blocks[i][0] + blocks[i][1] == blocks[i + 1][0] for i in range(world - 1))
+        if T >= 4 * world:
+            assert all(b % 4 == 0 for b, _ in blocks)
+            assert all(c > 0 for _, c in blocks)
+        load = lambda bl: max((w[b:b + c].sum() for b, c in bl), default=0.0)   # noqa: E731
+        assert load(blocks) <= load(row_blocks(T, world)) + 1e-9
+    # a ramp: the even split is 1.75x the mean at 8 blocks, the balanced one within a few percent
+    w = np.arange(1024.0) + 1
+    blocks = balanced_row_blocks(w, 8)
+    assert max(w[b:b + c].sum() for b, c in blocks) <= 1.05 * w.sum() / 8
+    assert balanced_row_blocks(np.zeros(64), 4) == row_blocks(64, 4)
+
+
+def _worker_balanced(rank, world, port, n, tau, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cuspamm_b200 import ShardedSpamm, balanced_row_blocks
+
+        A = signed_decay(n, 0.04, 31)
+        A[: n // 4] *= np.float32(50.0)          # the first quarter of the rows keeps far more products
+        B = signed_decay(n, 0.05, 32)
+
+        def run(blocks):
+            sh = ShardedSpamm(n, n, n, plan_factory=CpuPlan, blocks=blocks)
+            b, c = sh.row_tile_begin, sh.row_tile_count
+            sh.distribute(np.ascontiguousarray(A[b * 32:(b + c) * 32]), B if rank == 0 else None)
+            sh.run(tau)
+            return sh
+
+        sh = run(None)
+        per_row = sh.row_survivors()
+        assert per_row.shape == (n // 32,) and int(per_row.sum()) == sh.survivors()
+        blocks = balanced_row_blocks(per_row + 1.0, world)
+        assert blocks != sh.blocks and blocks[0][1] < sh.blocks[0][1]      # the heavy rows get the smaller block
+        sh2 = run(blocks)
+        assert sh2.survivors() == sh.survivors()
+        full = sh2.gather_c(0)
+        if rank == 0:
+            np.save(os.path.join(out_dir, "C.npy"), full.numpy())
+            np.save(os.path.join(out_dir, "blocks.npy"), np.array(blocks))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_survivor_balanced_partition_gives_the_same_product(tmp_path, oracle):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    n, tau, world = 512, 50.0, 2
+    mp.spawn(_worker_balanced, args=(world, port, n, tau, str(tmp_path)), nprocs=world, join=True)
+    A = signed_decay(n, 0.04, 31)
+    A[: n // 4] *= np.float32(50.0)
+    B = signed_decay(n, 0.05, 32)
+    C_ref, _ = oracle.spamm(A, B, tau)
+    assert np.array_equal(np.load(tmp_path / "C.npy"), C_ref)
+    blocks = np.load(tmp_path / "blocks.npy")
+    assert blocks[0][1] != blocks[1][1]
