@@ -47,6 +47,7 @@ SIGNATURES = {
     "spamm_plan_set_chunk_tiles": (_i, [_vp, _i]),
     "spamm_plan_set_pack_mode": (_i, [_vp, _i]),
     "spamm_clear_c_early": (_i, [_vp]),
+    "spamm_plan_set_precision": (_i, [_vp, _i]),
     "spamm_norms": (_i, [_vp]),
     "spamm_norms_share": (_i, [_vp, _i, _i]),
     "spamm_norm_b_share": (_i, [_vp, _i, _i]),

@@ -66,11 +66,14 @@ int build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_til
                        cudaStream_t stream);
 int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
                      const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
-                     bool reset_queues, cudaStream_t stream);
+                     void *d_low_a, void *d_low_b, bool reset_queues, cudaStream_t stream);
 int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                           const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                           spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                          int64_t ldc, bool reset_queues, bool try_pairs, bool c_zeroed, cudaStream_t stream);
+                          int64_t ldc, bool reset_queues, bool try_pairs, int mode, cudaStream_t stream);
+// `mode` of gated_multiply_launch, a sum of:
+constexpr int GM_C_ZEROED = 1;      // C was cleared beforehand (or holds a partial result): macro tiles without steps are left alone
+constexpr int GM_ACCUMULATE = 2;    // the products are added to what C holds instead of replacing it
 
 int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const int32_t *d_step_counts,
                                spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,

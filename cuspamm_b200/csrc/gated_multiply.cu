@@ -91,8 +91,10 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                       const uint32_t *__restrict__ steps, const int32_t *__restrict__ step_counts,
                       const int32_t *__restrict__ order, const int32_t *__restrict__ busy_list,
                       spamm_list_scalars *__restrict__ sc, int row_tiles, int k_tiles, int n_tiles,
-                      float *__restrict__ c, int64_t ldc, int pairs_launched, int c_zeroed)
+                      float *__restrict__ c, int64_t ldc, int pairs_launched, int mode)
 {
+    const bool c_zeroed = (mode & GM_C_ZEROED) != 0;        // leave macro tiles without steps alone
+    const bool accumulate = (mode & GM_ACCUMULATE) != 0;    // add to C
     extern __shared__ uint8_t smem_raw[];
     // stage data first (128-byte aligned), control block after it
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -500,7 +502,8 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 tmem_ld32(taddr, v);
                 tmem_wait_ld();
                 tmem_st32_zero(taddr);
-                if (row_ok && mj * MT_C + cc < n_tiles) store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane);
+                if (row_ok && mj * MT_C + cc < n_tiles)
+                    store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane, accumulate);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -526,15 +529,18 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
                                         int k_tiles, int n_tiles, float *d_c, int64_t ldc, void *stream)
 {
     return spamm::gated_multiply_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_order, d_busy_list, d_scalars,
-                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, true, false, (cudaStream_t)stream);
+                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, true, 0, (cudaStream_t)stream);
 }
 
 int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                                  const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                                  spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                                 int64_t ldc, bool reset_queues, bool try_pairs, bool c_zeroed, cudaStream_t stream)
+                                 int64_t ldc, bool reset_queues, bool try_pairs, int mode, cudaStream_t stream)
 {
     using namespace spamm;
+    // adding to C only makes sense where C is not overwritten with zeros, and never through the paired kernel
+    if (mode < 0 || mode > (GM_C_ZEROED | GM_ACCUMULATE) || ((mode & GM_ACCUMULATE) && (!(mode & GM_C_ZEROED) || try_pairs)))
+        return SPAMM_ERR_INVALID;
     if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
         k_tiles < 0 || n_tiles < 0 || ldc < (int64_t)n_tiles * TILE || (ldc & 3) ||
         (reinterpret_cast<uintptr_t>(d_c) & 15) || (reinterpret_cast<uintptr_t>(d_half_a) & 15) ||
@@ -571,7 +577,7 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
     gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, stream>>>(
         static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
-        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, try_pairs ? 1 : 0, c_zeroed ? 1 : 0);
+        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, try_pairs ? 1 : 0, mode);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -15,6 +15,9 @@
 
 namespace spamm {
 
+// the part of x that its half rounding leaves over (exact in float; rounded to half once more when stored)
+__device__ __forceinline__ float half_residual(float x) { return x - __half2float(__float2half_rn(x)); }
+
 __device__ __forceinline__ uint4 pack8(const float *f)
 {
     __half2 h0 = __floats2half2_rn(f[0], f[1]);
@@ -32,8 +35,11 @@ __device__ __forceinline__ uint4 pack8(const float *f)
 __global__ void __launch_bounds__(256)
 pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k_tiles, int n_tiles,
                  const uint32_t *__restrict__ tile_list, spamm_list_scalars *__restrict__ sc,
-                 uint8_t *__restrict__ half_a, uint8_t *__restrict__ half_b, int reset_queues)
+                 uint8_t *__restrict__ half_a, uint8_t *__restrict__ half_b, uint8_t *__restrict__ low_a,
+                 uint8_t *__restrict__ low_b, int reset_queues)
 {
+    // low_a / low_b (both or neither): second set of packed tiles holding half(x - half(x)), same layout and
+    // slab order, for the split-precision mode
     // optional: the multiply kernel (next on the stream) starts its two work counters from zero
     if (reset_queues && blockIdx.x == 0 && threadIdx.x < 2) (&sc->queue_busy)[threadIdx.x] = 0u;
     __shared__ float tr[8][TILE][TILE + 1];
@@ -62,7 +68,14 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k
                 const float4 lo = *reinterpret_cast<const float4 *>(src + (int64_t)row * K + kg * 8);
                 const float4 hi = *reinterpret_cast<const float4 *>(src + (int64_t)row * K + kg * 8 + 4);
                 const float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                *reinterpret_cast<uint4 *>(dst + (row >> 3) * 512 + kg * 128 + (row & 7) * 16) = pack8(f);
+                const int off = (row >> 3) * 512 + kg * 128 + (row & 7) * 16;
+                *reinterpret_cast<uint4 *>(dst + off) = pack8(f);
+                if (low_a) {
+                    float g[8];
+#pragma unroll
+                    for (int x = 0; x < 8; x++) g[x] = half_residual(f[x]);
+                    *reinterpret_cast<uint4 *>(low_a + slab * A_SLAB_BYTES + sub * TILE_BYTES + off) = pack8(g);
+                }
             }
             cnt_a++;
         } else {
@@ -78,7 +91,14 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k
                 float f[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) f[x] = tr[warp][kg * 8 + x][lane];
-                *reinterpret_cast<uint4 *>(dst + (lane >> 3) * 512 + kg * 128 + (lane & 7) * 16) = pack8(f);
+                const int off = (lane >> 3) * 512 + kg * 128 + (lane & 7) * 16;
+                *reinterpret_cast<uint4 *>(dst + off) = pack8(f);
+                if (low_b) {
+                    float g[8];
+#pragma unroll
+                    for (int x = 0; x < 8; x++) g[x] = half_residual(f[x]);
+                    *reinterpret_cast<uint4 *>(low_b + slab * B_SLAB_BYTES + sub * TILE_BYTES + off) = pack8(g);
+                }
             }
             cnt_b++;
         }
@@ -99,19 +119,21 @@ extern "C" int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_t
                                    void *d_half_b, void *stream)
 {
     return spamm::pack_half_launch(d_a, d_b, row_tiles, k_tiles, n_tiles, d_tile_list, d_scalars, d_half_a, d_half_b,
-                                   false, (cudaStream_t)stream);
+                                   nullptr, nullptr, false, (cudaStream_t)stream);
 }
 
 int spamm::pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
                             const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
-                            bool reset_queues, cudaStream_t stream)
+                            void *d_low_a, void *d_low_b, bool reset_queues, cudaStream_t stream)
 {
     using namespace spamm;
     if (!d_a || !d_b || !d_tile_list || !d_scalars || !d_half_a || !d_half_b || row_tiles < 0 || k_tiles < 0 ||
         n_tiles < 0)
         return SPAMM_ERR_INVALID;
     if ((reinterpret_cast<uintptr_t>(d_a) & 15) || (reinterpret_cast<uintptr_t>(d_b) & 15) ||
-        (reinterpret_cast<uintptr_t>(d_half_a) & 15) || (reinterpret_cast<uintptr_t>(d_half_b) & 15))
+        (reinterpret_cast<uintptr_t>(d_half_a) & 15) || (reinterpret_cast<uintptr_t>(d_half_b) & 15) ||
+        (reinterpret_cast<uintptr_t>(d_low_a) & 15) || (reinterpret_cast<uintptr_t>(d_low_b) & 15) ||
+        ((d_low_a == nullptr) != (d_low_b == nullptr)))
         return SPAMM_ERR_INVALID;
     const int64_t total = ((int64_t)ceil_div(row_tiles, MT_R) * MT_R + (int64_t)ceil_div(n_tiles, MT_C) * MT_C) * k_tiles;
     if (total == 0) return SPAMM_OK;
@@ -121,7 +143,8 @@ int spamm::pack_half_launch(const float *d_a, const float *d_b, int row_tiles, i
     if (blocks > max_blocks) blocks = max_blocks;
     pack_half_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
         d_a, d_b, k_tiles, n_tiles, d_tile_list, d_scalars, static_cast<uint8_t *>(d_half_a),
-        static_cast<uint8_t *>(d_half_b), reset_queues ? 1 : 0);
+        static_cast<uint8_t *>(d_half_b), static_cast<uint8_t *>(d_low_a), static_cast<uint8_t *>(d_low_b),
+        reset_queues ? 1 : 0);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -44,6 +44,8 @@ struct spamm_plan {
     int32_t *d_counts = nullptr, *d_step_counts = nullptr;
     uint32_t *d_steps = nullptr;
     uint8_t *d_half_a = nullptr, *d_half_b = nullptr;
+    uint8_t *d_low_a = nullptr, *d_low_b = nullptr;     // split precision: packed half(x - half(x)), allocated on demand
+    int precision = SPAMM_PRECISION_HALF;
     int32_t *d_order = nullptr;         // macro-tile visiting order of the multiply kernel
     int32_t *d_busy = nullptr;          // macro tiles that have steps
     uint32_t *d_tile_list = nullptr;    // tiles to convert to half
@@ -209,6 +211,23 @@ static int setup_chunk_orders(spamm_plan *p)
 
 extern "C" {
 
+int spamm_plan_set_precision(spamm_plan *p, int precision)
+{
+    if (!p || (precision != SPAMM_PRECISION_HALF && precision != SPAMM_PRECISION_SPLIT)) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    if (precision == SPAMM_PRECISION_SPLIT && !p->d_low_a) {
+        int st;
+        if ((st = dev_alloc(&p->d_low_a, p->bytes_half_a()))) return st;
+        if ((st = dev_alloc(&p->d_low_b, p->bytes_half_b()))) return st;
+    }
+    if (precision != p->precision) {
+        p->have_pack = false;       // the packed tiles belong to the other mode
+        p->packed_all = false;      // the norm pass converts high parts only: spamm_pack must run
+    }
+    p->precision = precision;
+    return SPAMM_OK;
+}
+
 int spamm_plan_set_pack_mode(spamm_plan *p, int mode)
 {
     if (!p || (mode != SPAMM_PACK_AUTO && mode != SPAMM_PACK_LISTED && mode != SPAMM_PACK_ALL)) return SPAMM_ERR_INVALID;
@@ -351,6 +370,7 @@ int spamm_plan_destroy(spamm_plan *p)
     if (p->h_peer_error) cudaFreeHost(p->h_peer_error);
     cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
     cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared); cudaFree(p->d_order);
+    cudaFree(p->d_low_a); cudaFree(p->d_low_b);
     cudaFree(p->d_busy); cudaFree(p->d_tile_list); cudaFree(p->d_list_scratch);
     cudaFree(p->d_cv_scratch); cudaFree(p->d_cv_count); cudaFree(p->d_err_scratch);
     if (p->h_scalars) cudaFreeHost(p->h_scalars);
@@ -503,7 +523,8 @@ int spamm_norms(spamm_plan *p)
     if (p->row_tiles == 0) return spamm_norms_share(p, 0, p->k_tiles);
     DeviceGuard guard(p->device);
     // both maps in one launch; with the conversion of every tile to half when most tiles are going to be needed
-    const bool all = p->pack_mode == SPAMM_PACK_ALL || (p->pack_mode == SPAMM_PACK_AUTO && p->pack_all_hint == 1);
+    const bool all = p->precision == SPAMM_PRECISION_HALF &&
+                     (p->pack_mode == SPAMM_PACK_ALL || (p->pack_mode == SPAMM_PACK_AUTO && p->pack_all_hint == 1));
     int st = all ? norm_pack_pair_launch(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->d_half_a, p->d_b,
                                          p->K, p->N, p->N, p->d_norm_b, p->d_half_b, p->stream)
                  : spamm_norm_map_pair_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, p->d_b, p->K, p->N,
@@ -580,8 +601,10 @@ int spamm_pack(spamm_plan *p)
     if (!p->have_lists) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     if (p->row_tiles && !p->packed_all) {
+        const bool split = p->precision == SPAMM_PRECISION_SPLIT;
         int st = pack_half_launch(p->d_a, p->d_b, p->row_tiles, p->k_tiles, p->n_tiles, p->d_tile_list, p->scalars(),
-                                  p->d_half_a, p->d_half_b, true, p->stream);
+                                  p->d_half_a, p->d_half_b, split ? p->d_low_a : nullptr, split ? p->d_low_b : nullptr,
+                                  true, p->stream);
         if (st) return st;
         p->launches++;
         p->queues_clean = true;
@@ -601,10 +624,22 @@ int spamm_gated_multiply(spamm_plan *p)
         p->c_zero_pending = false;      // consumed: a second multiply on the same lists writes all of C itself
         int st = gated_multiply_launch(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
                                        p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N,
-                                       !p->queues_clean, p->dense_hint != 0, zeroed, p->stream);
+                                       !p->queues_clean, p->dense_hint != 0, zeroed ? GM_C_ZEROED : 0, p->stream);
         p->queues_clean = false;
         if (st) return st;
         p->launches++;
+        if (p->precision == SPAMM_PRECISION_SPLIT) {
+            // x = hi + lo per operand: hi*hi is in C; hi*lo and lo*hi are added by two more passes over the same
+            // lists (lo*lo, 2^-22 of the result, is dropped)
+            for (int pass = 0; pass < 2; pass++) {
+                st = gated_multiply_launch(pass == 0 ? p->d_half_a : p->d_low_a, pass == 0 ? p->d_low_b : p->d_half_b,
+                                           p->d_steps, p->d_step_counts, p->d_order, p->d_busy, p->scalars(),
+                                           p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, true, false,
+                                           GM_C_ZEROED | GM_ACCUMULATE, p->stream);
+                if (st) return st;
+                p->launches++;
+            }
+        }
     }
     return SPAMM_OK;
 }
@@ -738,13 +773,24 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
                                     p->d_tile_list, p->d_busy + mt0, sc, stream)))
         return st;
     uint8_t *half_a = p->d_half_a + mi0 * p->k_tiles * A_SLAB_BYTES;
-    if ((st = pack_half_launch(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b, true,
-                               stream)))
+    const bool split = p->precision == SPAMM_PRECISION_SPLIT;
+    uint8_t *low_a = split ? p->d_low_a + mi0 * p->k_tiles * A_SLAB_BYTES : nullptr;
+    if ((st = pack_half_launch(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b, low_a,
+                               split ? p->d_low_b : nullptr, true, stream)))
         return st;
     if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->dense_hint != 0, false, stream)))
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->dense_hint != 0, 0, stream)))
         return st;
+    for (int pass = 0; split && pass < 2; pass++) {
+        if ((st = gated_multiply_launch(pass == 0 ? half_a : low_a, pass == 0 ? p->d_low_b : p->d_half_b,
+                                        p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0, d_order,
+                                        p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
+                                        p->d_c + (size_t)t0 * TILE * p->N, p->N, true, false,
+                                        GM_C_ZEROED | GM_ACCUMULATE, stream)))
+            return st;
+        p->launches++;
+    }
     p->launches += do_norm ? 5 : 4;
     return SPAMM_OK;
 }

@@ -139,8 +139,9 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 constexpr int EPI_ROW_BYTES = 144;
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;          // 4608 bytes per epilogue warp
 
+// With `add` the block is added to what C holds (float addition, C's value first).
 __device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const uint32_t *v, float *c_block,
-                                                      int64_t ldc, int lane)
+                                                      int64_t ldc, int lane, bool add = false)
 {
     uint4 *mine = reinterpret_cast<uint4 *>(warp_tile + lane * EPI_ROW_BYTES);
 #pragma unroll
@@ -150,8 +151,16 @@ __device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const 
 #pragma unroll
     for (int r0 = 0; r0 < 32; r0 += 4) {
         const int r = r0 + sub;
-        const float4 o = *reinterpret_cast<const float4 *>(warp_tile + r * EPI_ROW_BYTES + part * 16);
-        __stcs(reinterpret_cast<float4 *>(c_block + (int64_t)r * ldc + part * 4), o);
+        float4 o = *reinterpret_cast<const float4 *>(warp_tile + r * EPI_ROW_BYTES + part * 16);
+        float4 *dst = reinterpret_cast<float4 *>(c_block + (int64_t)r * ldc + part * 4);
+        if (add) {
+            const float4 old = *dst;
+            o.x = old.x + o.x;
+            o.y = old.y + o.y;
+            o.z = old.z + o.z;
+            o.w = old.w + o.w;
+        }
+        __stcs(dst, o);
     }
     __syncwarp();
 }

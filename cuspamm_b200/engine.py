@@ -232,6 +232,15 @@ class SpammPlan:
     def run(self, tau: float) -> None:
         check(self._lib.spamm_run(self._h, float(tau)), "spamm_run")
 
+    def set_precision(self, precision: str) -> None:
+        """"half" (default: operands rounded to half, the reference's tensor-core build) or "split" (each operand
+        as a sum of two halves, three tensor-core passes: float-level accuracy, the stand-in for the reference's
+        float build)."""
+        modes = {"half": 0, "split": 1}
+        if precision not in modes:
+            raise ValueError(f"precision must be one of {sorted(modes)}")
+        check(self._lib.spamm_plan_set_precision(self._h, modes[precision]), "spamm_plan_set_precision")
+
     def clear_c_early(self) -> None:
         """Announce that lists, pack and multiply follow: C may be cleared now on the second stream (a speed hint)."""
         check(self._lib.spamm_clear_c_early(self._h), "spamm_clear_c_early")

@@ -189,6 +189,21 @@ int spamm_multiply(spamm_plan *plan, const float *a_rows, const float *b, float 
 int spamm_plan_set_chunk_tiles(spamm_plan *plan, int tiles);
 
 /*
+ * Precision of the tile products.
+ *   SPAMM_PRECISION_HALF   (default) operands rounded to half, float accumulation: the reference's tensor-core build
+ *                          (USINGHALF 1, cuSpAMM.cu:276-392).
+ *   SPAMM_PRECISION_SPLIT  float-level accuracy on the tensor cores, in place of the reference's CUDA-core float
+ *                          build (USINGHALF 0: cuSpAMM.cu:126-274).  Every operand element x is split as
+ *                          hi = half(x), lo = half(x - hi); the product is hi*hi + hi*lo + lo*hi, three tensor-core
+ *                          passes over the same lists, float accumulation (lo*lo, about 2^-22 of the result, is
+ *                          dropped; elements below 6e-8 in magnitude have no low part).  Norm maps and lists are the
+ *                          same in both modes; the multiply takes about three times as long.
+ * Takes effect at the next spamm_pack; allocates a second set of packed-tile buffers the first time.
+ */
+enum { SPAMM_PRECISION_HALF = 0, SPAMM_PRECISION_SPLIT = 1 };
+int spamm_plan_set_precision(spamm_plan *plan, int precision);
+
+/*
  * Optional, for callers that issue the steps one by one (spamm_run and spamm_finish do this themselves): announces
  * that the rest of a whole step (lists, pack, multiply) follows.  If the counters read back by the last spamm_sync /
  * spamm_run_timed showed that at most a quarter of the 128 x 256 blocks of C received any product, all of C is

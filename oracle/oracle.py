@@ -36,6 +36,8 @@ def lib() -> C.CDLL:
         L.oracle_fill_lists.restype, L.oracle_fill_lists.argtypes = None, [vp, vp, i, i, i, i, f, vp, vp]
         L.oracle_gated_multiply.restype = None
         L.oracle_gated_multiply.argtypes = [vp, vp, i, i, i, vp, vp, vp]
+        L.oracle_gated_multiply_exact.restype = None
+        L.oracle_gated_multiply_exact.argtypes = [vp, vp, i, i, i, vp, vp, vp]
         L.oracle_spamm.restype = i64
         L.oracle_spamm.argtypes = [vp, vp, vp, i, i, i, i, i, f, vp, vp, vp]
         L.oracle_gen_decay_exp.restype, L.oracle_gen_decay_exp.argtypes = None, [vp, f, f, i, i]
@@ -98,6 +100,28 @@ def gated_multiply(Ah_rows, Bh, offsets, kidx) -> np.ndarray:
     lib().oracle_gated_multiply(Ah_rows.ctypes.data, Bh.ctypes.data, K, N, rows // 32, offsets.ctypes.data, kp,
                                 Cm.ctypes.data)
     return Cm
+
+
+def gated_multiply_exact(A_rows, B, offsets, kidx) -> np.ndarray:
+    """The gated sum on the unrounded float inputs, double accumulation (checker of the split-precision mode)."""
+    A_rows, B = _f32(A_rows), _f32(B)
+    rows, K = A_rows.shape
+    N = B.shape[1]
+    Cm = np.empty((rows, N), dtype=np.float32)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int64)
+    kidx = np.ascontiguousarray(kidx, dtype=np.int32)
+    kp = kidx.ctypes.data if kidx.size else np.zeros(1, np.int32).ctypes.data
+    lib().oracle_gated_multiply_exact(A_rows.ctypes.data, B.ctypes.data, K, N, rows // 32, offsets.ctypes.data, kp,
+                                      Cm.ctypes.data)
+    return Cm
+
+
+def spamm_exact(A, B, tau: float):
+    """(C, S): same norm maps and lists as `spamm`, product of the unrounded inputs in double."""
+    A, B = _f32(A), _f32(B)
+    nA, nB = norm_map(A), norm_map(B)
+    counts, offsets, kidx = lists(nA, nB, tau)
+    return gated_multiply_exact(A, B, offsets, kidx), int(counts.sum())
 
 
 def spamm(A, B, tau: float, row_begin: int = 0, row_count=None, want_maps: bool = False):

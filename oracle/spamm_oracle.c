@@ -255,6 +255,42 @@ void oracle_gated_multiply(const float *Ah, const float *Bh, int K, int N,
 }
 
 /*
+ * The same gated sum on the UNROUNDED float inputs with double accumulation, rounded to float once at the end:
+ * what the reference's float build (USINGHALF 0: get_C_Threads1Element_Mul, cuSpAMM.cu:203-266) approximates with
+ * float accumulation on CUDA cores.  Checker for the split-precision mode of the library (three half products
+ * per tile product), which aims at float-level accuracy on tensor cores.
+ */
+void oracle_gated_multiply_exact(const float *A, const float *B, int K, int N,
+                                 int row_count, const int64_t *offsets,
+                                 const int32_t *kidx, float *C)
+{
+    int TN = N / TILE;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < row_count; i++) {
+        for (int j = 0; j < TN; j++) {
+            double acc[TILE][TILE];
+            memset(acc, 0, sizeof(acc));
+            int64_t t = (int64_t)i * TN + j;
+            for (int64_t o = offsets[t]; o < offsets[t + 1]; o++) {
+                int k = kidx[o];
+                const float *a = A + ((int64_t)i * TILE) * K + (int64_t)k * TILE;
+                const float *b = B + ((int64_t)k * TILE) * N + (int64_t)j * TILE;
+                for (int r = 0; r < TILE; r++) {
+                    for (int kk = 0; kk < TILE; kk++) {
+                        double av = (double)a[(int64_t)r * K + kk];
+                        const float *brow = b + (int64_t)kk * N;
+                        for (int c = 0; c < TILE; c++) acc[r][c] += av * (double)brow[c];
+                    }
+                }
+            }
+            for (int r = 0; r < TILE; r++)
+                for (int c = 0; c < TILE; c++)
+                    C[((int64_t)i * TILE + r) * N + (int64_t)j * TILE + c] = (float)acc[r][c];
+        }
+    }
+}
+
+/*
  * Whole path on host matrices: norm maps of the float data, lists, product of the
  * half-rounded data.  nA_out (row_count x TK, this row block only), nB_out (TK x TN)
  * and counts_out (row_count x TN) may be NULL.  Returns S (surviving tile products) or -1.

@@ -313,3 +313,51 @@ def test_c_cleared_early_with_cut_macro_tiles(oracle):
             assert p.counts()[1] == S
             assert rel_fro(C, C_ref) <= C_TOL
             assert not C.reshape(93, 32, 95, 32).transpose(0, 2, 1, 3)[counts == 0].any()
+
+
+def test_split_precision_reaches_float_accuracy(oracle):
+    """The float-accuracy mode (operands as sums of two halves, three tensor-core passes; stands in for the
+    reference's float build, cuSpAMM.cu:126-274): same norm maps and lists, C within 1e-5 relative Frobenius error of
+    the product of the UNROUNDED inputs accumulated in double, where the half mode is at 1e-4 ... 1e-3."""
+    from cuspamm_b200 import SpammPlan
+
+    n = 512
+    A = signed_decay(n, 0.02, seed=91)
+    B = signed_decay(n, 0.03, seed=92)
+    for tau in (0.0, 0.05, 1e9):
+        C_exact, S = oracle.spamm_exact(A, B, tau)
+        C_half_ref, S2 = oracle.spamm(A, B, tau)
+        assert S == S2
+        with SpammPlan(n, n, n) as p:
+            p.upload(A, B)
+            errs = {}
+            for mode in ("half", "split", "split", "half"):       # twice: the second step runs with refreshed hints
+                p.set_precision(mode)
+                p.run(tau)
+                p.sync()
+                assert p.counts()[1] == S
+                C = p.download_c()
+                if S == 0:
+                    assert not C.any()
+                    continue
+                errs.setdefault(mode, []).append(rel_fro(C, C_exact))
+                if mode == "half":
+                    assert rel_fro(C, C_half_ref) <= 2e-6
+        if S:
+            assert max(errs["split"]) <= 1e-5, errs
+            assert min(errs["half"]) > 10 * max(errs["split"]), errs
+    # the host-to-host call in chunks of rows, and a rectangular shape with cut macro tiles
+    rng = np.random.default_rng(23)
+    M, K, N = 160, 224, 352
+    A = (rng.standard_normal((M, K)) * np.exp(-rng.random((M, K)) * 5)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * np.exp(-rng.random((K, N)) * 5)).astype(np.float32)
+    tau = float(np.median(oracle.norm_map(A)[:, :, None] * oracle.norm_map(B)[None]))
+    C_exact, S = oracle.spamm_exact(A, B, tau)
+    with SpammPlan(M, K, N) as p:
+        p.set_precision("split")
+        p.set_chunk_tiles(4)
+        C, st = p.multiply(A, B, tau)
+        assert st["survivors"] == S and rel_fro(C, C_exact) <= 1e-5
+        p.set_chunk_tiles(64)
+        C, st = p.multiply(A, B, tau)
+        assert st["survivors"] == S and rel_fro(C, C_exact) <= 1e-5
