@@ -221,6 +221,8 @@ def run_ours(args):
 
     sh = ShardedSpamm(n, n, n, exchange=args.exchange)
     plan = sh.plan
+    if args.precision != "half":
+        plan.set_precision(args.precision)
     rows = plan.rows
     a_t, a_np = pinned((rows, n))
     generate_into(a_np, SEED_A, sh.row_tile_begin * 32, n)
@@ -253,6 +255,8 @@ def run_ours(args):
             del a_t, a_np
             sh = ShardedSpamm(n, n, n, exchange=args.exchange, blocks=blocks)
             plan = sh.plan
+            if args.precision != "half":
+                plan.set_precision(args.precision)
             rows = plan.rows
             a_t, a_np = pinned((rows, n))
             generate_into(a_np, SEED_A, sh.row_tile_begin * 32, n)
@@ -357,6 +361,24 @@ def run_ours(args):
     e2e_step()
     ms_e2e = timed(e2e_step, e2e_steps)
 
+    # ---- the same with the result left where it is computed: every rank copies its rows of C to its own pinned
+    # host buffer over its own PCIe link (what the reference's single-process form does per device); N > 1 only
+    ms_e2e_local = None
+    if world > 1:
+        from cuspamm_b200 import BUF_C
+
+        cl_t, _ = pinned((rows, n))
+
+        def e2e_local_step():
+            sh.distribute(a_np, b_np)
+            sh.run(tau)
+            with torch.cuda.stream(stream):
+                cl_t.copy_(plan.as_tensor(BUF_C), non_blocking=True)
+            sh.sync()
+
+        e2e_local_step()
+        ms_e2e_local = timed(e2e_local_step, e2e_steps)
+
     # ---- the reference's comparator (run_cublas_time, tool.cu:153-224): the dense half GEMM of the library on the
     # same matrices, same box (fp16 in, fp32 accumulate), single GPU only
     dense_gemm = None
@@ -429,7 +451,8 @@ def run_ours(args):
     line = {
         "metric": "spamm_executed_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f16xf16+f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f16xf16+f32" if args.precision == "half" else "2xf16 split, 3 products, +f32",
+        "data": "synthetic",
         "config": {"workload": workload_name(n, tau), "survivors": S, "executed_fraction": S / (n // 32) ** 3,
                    "timed_region": "norm maps + skip lists + half packing + gated multiply, inputs resident in HBM",
                    "l2": "inputs (2*4*N^2 bytes) larger than L2, no flush needed", "parallelism": f"rowblock{world}",
@@ -447,6 +470,11 @@ def run_ours(args):
         line["dense_tau0"] = dense_multi
     if dense_gemm is not None:
         line["dense_gemm"] = dense_gemm
+    if ms_e2e_local is not None:
+        line["e2e_rank_local_output"] = {"value": 65536.0 * S / (ms_e2e_local * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                         "ms_per_step": ms_e2e_local,
+                                         "note": "as e2e, but every rank copies its rows of C to its own host buffer "
+                                                 "instead of gathering C on rank 0 first"}
     if phase is not None and world == 1:
         norm_bytes = 8.0 * n * n   # every float of A and of B read once
         # when the lists name most tiles the norm pass also writes every tile as half (2 bytes per element)
@@ -519,6 +547,8 @@ def main():
     ap.add_argument("--tau", type=float, default=None)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--precision", default="half", choices=["half", "split"],
+                    help="half: the metric's configuration; split: the float-accuracy mode (three tensor-core passes)")
     ap.add_argument("--partition", default="auto", choices=["auto", "even", "balanced"],
                     help="row blocks of C per GPU: even (the reference's), or moved so that the surviving products "
                          "are spread evenly (auto: only when that lowers the largest block's work by more than 3 %%)")
