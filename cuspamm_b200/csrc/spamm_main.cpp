@@ -3,7 +3,10 @@
 // time.  What para.h fixes at compile time is a command-line option here:
 //
 //   spamm_main [--n N | --m M --k K --nn N] [--devices D] [--tau T] [--iters I] [--warmup W]
-//              [--matrix alg|exp|sexp|ualg|uniform] [--tune RATE]
+//              [--matrix alg|exp|sexp|ualg|uniform] [--tune RATE] [--float]
+//
+// --float is the counterpart of building the reference with USINGHALF 0 (para.h): float-level accuracy, here through
+// the split-precision mode on the tensor cores.
 //
 // Defaults are the reference's: 2048^3, one device, tau = 1.548969, algebraic decay c=v=0.1, 10 iterations of which
 // the first 5 are warm-up (para.h:1-14).  Differences: the mean is the true mean over the timed iterations (the
@@ -31,6 +34,7 @@ int main(int argc, char **argv)
     int M = 2048, K = 2048, N = 2048, devices = 1, iters = 10, warmup = 5;
     double tau = 1.548969, tune = -1.0;
     std::string matrix = "alg";
+    bool split = false;
     for (int i = 1; i < argc; i++) {
         auto next = [&](const char *name) -> const char * {
             if (i + 1 >= argc) { fprintf(stderr, "%s needs a value\n", name); exit(2); }
@@ -46,12 +50,13 @@ int main(int argc, char **argv)
         else if (!strcmp(argv[i], "--warmup")) warmup = atoi(next("--warmup"));
         else if (!strcmp(argv[i], "--matrix")) matrix = next("--matrix");
         else if (!strcmp(argv[i], "--tune")) tune = atof(next("--tune"));
+        else if (!strcmp(argv[i], "--float")) split = true;
         else { fprintf(stderr, "unknown option %s\n", argv[i]); return 2; }
     }
     // the reference pads to multiples of 32 (main.h:54-56)
     const int Mp = (M + 31) / 32 * 32, Kp = (K + 31) / 32 * 32, Np = (N + 31) / 32 * 32;
-    printf("input parameters: M=%d K=%d N=%d Norm=%f USINGHALF=1 devices=%d matrix=%s\n", Mp, Kp, Np, tau, devices,
-           matrix.c_str());
+    printf("input parameters: M=%d K=%d N=%d Norm=%f USINGHALF=%d devices=%d matrix=%s\n", Mp, Kp, Np, tau,
+           split ? 0 : 1, devices, matrix.c_str());
     const int row_tiles = Mp / 32;
     if (devices <= 0 || iters <= warmup || row_tiles / devices <= 0) {
         printf("PART error! too many parts!\n");
@@ -80,6 +85,8 @@ int main(int argc, char **argv)
         count[d] = (d == devices - 1) ? row_tiles - b : row_tiles / devices;
         b += count[d];
         if ((st = spamm_plan_create(&plan[d], Mp, Kp, Np, begin[d], count[d], d))) return fail("spamm_plan_create", st);
+        if (split && (st = spamm_plan_set_precision(plan[d], SPAMM_PRECISION_SPLIT)))
+            return fail("spamm_plan_set_precision", st);
         if ((st = spamm_upload(plan[d], h_A + (size_t)begin[d] * 32 * Kp, h_B))) return fail("spamm_upload", st);
     }
     float norm = (float)tau;
