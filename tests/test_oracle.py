@@ -160,3 +160,35 @@ def test_tuner_reaches_the_expected_rate(oracle):
     tau, rate, iters = oracle.tune_valid_rate(nA, nA, 0.75, 20, 0.01)
     assert abs(rate - 0.75) < 0.01 and 0 < iters < 20
     assert abs(np_mask(nA, nA, tau).mean() - 0.75) < 0.011
+
+
+def test_exact_product_is_the_double_precision_gated_sum(oracle):
+    """The checker of the split-precision mode: same lists as the half-precision checker, product of the unrounded
+    inputs accumulated in double and rounded once."""
+    rng = np.random.default_rng(41)
+    A = (rng.standard_normal((96, 128)) * np.exp(-rng.random((96, 128)) * 4)).astype(np.float32)
+    B = (rng.standard_normal((128, 160)) * np.exp(-rng.random((128, 160)) * 4)).astype(np.float32)
+    # tau = 0: the plain product
+    C0, S0 = oracle.spamm_exact(A, B, 0.0)
+    assert S0 == 3 * 4 * 5
+    # (the order of the double additions may differ from numpy's: allow one float rounding)
+    np.testing.assert_allclose(C0, (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32), rtol=2e-7, atol=1e-9)
+    # a threshold that drops about half of the tile products: tile by tile against numpy on the surviving k
+    nA, nB = oracle.norm_map(A), oracle.norm_map(B)
+    tau = float(np.median(nA[:, :, None] * nB[None]))
+    C, S = oracle.spamm_exact(A, B, tau)
+    C_half, S_half = oracle.spamm(A, B, tau)
+    assert S == S_half and 0 < S < S0
+    keep = (nA[:, :, None] * nB[None]) >= np.float32(tau)
+    ref = np.zeros((96, 160), dtype=np.float64)
+    for i in range(3):
+        for j in range(5):
+            for k in range(4):
+                if keep[i, k, j]:
+                    ref[i * 32:(i + 1) * 32, j * 32:(j + 1) * 32] += (
+                        A[i * 32:(i + 1) * 32, k * 32:(k + 1) * 32].astype(np.float64)
+                        @ B[k * 32:(k + 1) * 32, j * 32:(j + 1) * 32].astype(np.float64))
+    np.testing.assert_allclose(C, ref.astype(np.float32), rtol=2e-7, atol=1e-9)
+    # and the half-precision checker is a few 1e-4 away from it, as half rounding predicts
+    err = np.linalg.norm(C_half - C) / np.linalg.norm(C)
+    assert 1e-5 < err < 2e-3
