@@ -61,6 +61,8 @@ struct spamm_plan {
     cudaEvent_t ev[8] = {};
     cudaStream_t stream_d2h = nullptr;  // second stream: copies C chunks out while the next chunk is computed
     cudaEvent_t ev_chunk[MAX_CHUNKS] = {};
+    cudaStream_t stream_h2d = nullptr;  // third stream: uploads of the pipelined spamm_multiply, back to back
+    cudaEvent_t ev_up[MAX_CHUNKS + 2] = {};      // [c]: rows of chunk c are on the GPU; [MAX_CHUNKS]: B is; [+1]: entry fence
     cudaEvent_t ev_zero[2] = {};        // fork / join of the early clearing of C on the second stream
     int zero_hint = -1;                 // last counters read: did at most a quarter of the macro tiles have steps
     bool c_zero_pending = false;        // C is being cleared on the second stream; the multiply writes busy tiles only
@@ -68,8 +70,8 @@ struct spamm_plan {
     int n_chunks = 1;
     int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
 
-    int active_scalars = 1;
-    bool queues_clean = false;
+    int active_scalars = 1;             // how many sets of counters the last operation used (one per chunk)
+    bool queues_clean = false;          // the multiply's two work counters are zero (cleared by the list build or the packing kernel)
     int dense_hint = -1;                // last counters read: were at least half of the macro tiles dense (-1: unknown)
     int pack_mode = SPAMM_PACK_AUTO;    // which tiles are converted to half, see spamm_plan_set_pack_mode
     int pack_all_hint = -1;             // last counters read: did the lists name at least half of all tiles (-1: unknown)
@@ -84,7 +86,7 @@ struct spamm_plan {
     bool peer_wait_pending = false;
     void *peer_mapped[MAX_PEERS][3] = {};          // what cudaIpcOpenMemHandle returned, per peer
     float *peer_norm_b[MAX_PEERS][2] = {};
-    unsigned int *peer_flags[MAX_PEERS] = {};          // the packing kernel has reset the multiply's work counters             // how many scalar sets the last operation used
+    unsigned int *peer_flags[MAX_PEERS] = {};      // every peer's arrival flags, as mapped into this process
     bool have_norms = false, have_lists = false, have_pack = false;
     int64_t launches = 0;
 
@@ -283,13 +285,17 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
         if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) least = greatest = 0;
         const int main_priority = greatest < least ? least - 1 : least;
         if (cudaStreamCreateWithPriority(&p->stream, cudaStreamNonBlocking, main_priority) != cudaSuccess ||
-            cudaStreamCreateWithPriority(&p->stream_d2h, cudaStreamNonBlocking, least) != cudaSuccess)
+            cudaStreamCreateWithPriority(&p->stream_d2h, cudaStreamNonBlocking, least) != cudaSuccess ||
+            cudaStreamCreateWithPriority(&p->stream_h2d, cudaStreamNonBlocking, least) != cudaSuccess)
             return fail(record_cuda_error(cudaGetLastError(), "cudaStreamCreate"));
     }
     for (auto &e : p->ev_chunk)
         if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
             return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
     for (auto &e : p->ev_zero)
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
+            return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
+    for (auto &e : p->ev_up)
         if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
             return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
     {
@@ -381,8 +387,11 @@ int spamm_plan_destroy(spamm_plan *p)
         if (e) cudaEventDestroy(e);
     for (auto &e : p->ev_zero)
         if (e) cudaEventDestroy(e);
+    for (auto &e : p->ev_up)
+        if (e) cudaEventDestroy(e);
     cudaFree(p->d_order_chunk); cudaFree(p->d_order_last);
     if (p->stream_d2h) cudaStreamDestroy(p->stream_d2h);
+    if (p->stream_h2d) cudaStreamDestroy(p->stream_h2d);
     if (p->stream) cudaStreamDestroy(p->stream);
     delete p;
     return SPAMM_OK;
@@ -827,7 +836,21 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
     p->packed_all = false;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
     SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
-    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream));
+    // All uploads go back to back on their own stream (they start after everything already queued on the main
+    // stream, which may still read the old matrices); the main stream waits for B, then for each chunk of rows.
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[MAX_CHUNKS + 1], p->stream));
+    SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_h2d, p->ev_up[MAX_CHUNKS + 1], 0));
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream_h2d));
+    SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[MAX_CHUNKS], p->stream_h2d));
+    for (int c = 0; c < p->n_chunks; c++) {
+        const int t0 = c * p->chunk_tiles;
+        const int tiles = (c == p->n_chunks - 1) ? p->row_tiles - t0 : p->chunk_tiles;
+        const size_t a_off = (size_t)t0 * TILE * p->K;
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a + a_off, a_rows + a_off, sizeof(float) * (size_t)tiles * TILE * p->K,
+                                       cudaMemcpyHostToDevice, p->stream_h2d));
+        SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[c], p->stream_h2d));
+    }
+    SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_up[MAX_CHUNKS], 0));
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[0], p->stream));
     if ((st = spamm_norm_map_dev(p->d_b, p->K, p->N, p->N, p->d_norm_b, p->stream))) return st;
     p->launches++;
@@ -835,9 +858,8 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
     for (int c = 0; c < p->n_chunks; c++) {
         const int t0 = c * p->chunk_tiles;
         const int tiles = (c == p->n_chunks - 1) ? p->row_tiles - t0 : p->chunk_tiles;
-        const size_t a_off = (size_t)t0 * TILE * p->K, c_off = (size_t)t0 * TILE * p->N;
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a + a_off, a_rows + a_off, sizeof(float) * (size_t)tiles * TILE * p->K,
-                                       cudaMemcpyHostToDevice, p->stream));
+        const size_t c_off = (size_t)t0 * TILE * p->N;
+        SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_up[c], 0));
         if ((st = run_chunk(p, c, t0, tiles, tau, c == p->n_chunks - 1 ? p->d_order_last : p->d_order_chunk,
                             p->stream, true)))
             return st;
