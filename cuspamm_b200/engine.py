@@ -446,7 +446,9 @@ class ShardedSpamm:
                 self._nccl = self._dist.get_backend(self.group) == "nccl"
                 ts = getattr(self.plan, "torch_stream", None)
                 self._stream = ts() if ts is not None else None
-                self._side = self._torch.cuda.Stream(priority=-1) if self._nccl else None   # its blocks go first
+                # the exchange must outrank the plan's main stream (which is one step above the lowest priority), or
+                # its few blocks queue behind the norm kernel's; the runtime clamps the value to the highest priority
+                self._side = self._torch.cuda.Stream(priority=-5) if self._nccl else None
             nb, mine = self._nb, self._mine
             if self._nccl:
                 # this rank's share of B's map first, then its exchange on a side stream while A's map is computed
