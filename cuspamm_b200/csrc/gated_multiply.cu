@@ -7,19 +7,23 @@
 //
 //   warp 0      scheduler + producer: claims macro tiles from a device-wide work counter (those with steps first),
 //               publishes them to the other warps through a small ring, reads the macro tile's step list and
-//               issues bulk copies (cp.async.bulk, completion on
-//               an mbarrier) of the packed half tiles a step names into a ring of shared-memory stages;
-//   warp 1      one elected thread issues tcgen05.mma (M=128, N=32*run, K=16) per run of adjacent tile columns
-//               of a step; the step's row set becomes the instruction's disable-output-lane mask, so tile rows
-//               that did not survive are not touched -- no product outside the lists is ever added;
+//               issues bulk copies (cp.async.bulk, completion on an mbarrier) of the packed half tiles the steps
+//               name into a ring of shared-memory stages; the steps of one k share their copies;
+//   warp 1      the whole warp follows the stages, lane 0 issues tcgen05.mma (M=128, N=32*run, K=16) per run of
+//               adjacent tile columns of a step; the step's row set becomes the instruction's disable-output-lane
+//               mask, so tile rows that did not survive are not touched -- no product outside the lists is ever
+//               added;
 //   warps 6-9   fillers: when few macro tiles have steps, write the all-zero macro tiles from the start, in
 //               parallel with the pipeline;
-//   warps 2-5   epilogue: read the 128x256 float accumulator from tensor memory (tcgen05.ld), store it to C,
-//               clear it for the next macro tile; macro tiles without any step are written as zeros directly.
+//   warps 2-5   epilogue: read the 128x256 float accumulator from tensor memory (tcgen05.ld), turn it through a
+//               small shared-memory tile so that whole rows are stored to C, clear it for the next macro tile;
+//               macro tiles without any step are written as zeros directly.
 //
 // Two accumulators (2 x 256 of the 512 tensor-memory columns) let the epilogue of one macro tile overlap the
-// multiplies of the next.  Every wait on an mbarrier is bounded in time; when one runs out the block sets the
-// error word, drains its copies and multiplies, frees its tensor memory and returns.
+// multiplies of the next.  Two options serve the callers: macro tiles without steps can be left alone (C was cleared
+// beforehand, or holds a partial result), and the products can be added to C instead of replacing it (the second and
+// third pass of the split-precision mode).  Every wait on an mbarrier is bounded in time; when one runs out the
+// block sets the error word, drains its copies and multiplies, frees its tensor memory and returns.
 #include "tc_utils.cuh"
 
 namespace spamm {
