@@ -183,3 +183,29 @@ def test_survivor_balanced_partition_gives_the_same_product(tmp_path, oracle):
     assert np.array_equal(np.load(tmp_path / "C.npy"), C_ref)
     blocks = np.load(tmp_path / "blocks.npy")
     assert blocks[0][1] != blocks[1][1]
+
+
+def test_balanced_row_blocks_random_weights():
+    """Property check over random weight vectors: a complete contiguous split that is never worse than the even one,
+    and within one unit's weight of the ideal share."""
+    from hypothesis import given, settings, strategies as st
+
+    from cuspamm_b200 import balanced_row_blocks, row_blocks
+
+    @settings(max_examples=200, deadline=None, derandomize=True)
+    @given(st.lists(st.floats(min_value=0.0, max_value=1e6, allow_nan=False), min_size=1, max_size=300),
+           st.integers(min_value=1, max_value=8))
+    def check(weights, world):
+        w = np.asarray(weights, dtype=np.float64)
+        T = len(w)
+        blocks = balanced_row_blocks(w, world)
+        assert len(blocks) == world and blocks[0][0] == 0 and sum(c for _, c in blocks) == T
+        assert all(c >= 0 for _, c in blocks)
+        assert all(blocks[i][0] + blocks[i][1] == blocks[i + 1][0] for i in range(world - 1))
+        load = lambda bl: max((w[b:b + c].sum() for b, c in bl), default=0.0)   # noqa: E731
+        assert load(blocks) <= load(row_blocks(T, world)) * (1 + 1e-9) + 1e-9
+        unit = 4 if T >= 4 * world else 1
+        heaviest_unit = max(w[u:u + unit].sum() for u in range(0, T, unit))
+        assert load(blocks) <= w.sum() / world + heaviest_unit + 1e-6 * max(1.0, w.sum())
+
+    check()
