@@ -374,6 +374,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                     last = ctrl->stage_last[s] != 0u;
                     const uint32_t a_stage = stage0 + s * STAGE_BYTES;
                     const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+                    __syncwarp();       // every lane has read the stage's control words before lane 0 can release it
                     if (lane == 0) {
 #pragma unroll
                     for (int t = 0; t < SPS; t++) {
