@@ -2,6 +2,8 @@
 """Benchmark of the SpAMM hot path (norm maps -> skip lists -> half packing -> gated tensor-core multiply).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--n SIZE] [--tau TAU]
+                    [--workload exp|alg|lattice|dense] [--precision half|split] [--partition auto|even|balanced]
+                    [--exchange nccl|push] [--no-sweep] [--no-cpu]
 
 One "step" is one pass of the reference's timed region (cuSpAMM.cu:458-546) over matrices that are already
 resident in HBM.  The workload is the configuration the headline metric is quoted on: N=16384, exponential decay
@@ -249,7 +251,7 @@ def run_ours(args):
         weights = per_row + base
         load = lambda bl: max(weights[b:b + c].sum() for b, c in bl)       # noqa: E731
         blocks = balanced_row_blocks(weights, world)
-        if blocks != sh.blocks and load(blocks) < 0.97 * load(sh.blocks):
+        if blocks != sh.blocks and (args.partition == "balanced" or load(blocks) < 0.97 * load(sh.blocks)):
             imbalance = (load(sh.blocks) / (weights.sum() / world), load(blocks) / (weights.sum() / world))
             sh.close()
             del a_t, a_np
