@@ -90,6 +90,7 @@ SIGNATURES = {
     "spamm_macro_tile_order": (_i, [_i, _i, _vp]),
     "spamm_gen_decay_exp": (_i, [_vp, _f, _f, _i64, _i64, _i64]),
     "spamm_gen_decay_alg": (_i, [_vp, _f, _f, _i64, _i64, _i64]),
+    "spamm_gen_ones": (_i, [_vp, _i64, _i64, _i64]),
     "spamm_gen_signed_exp": (_i, [_vp, C.c_double, C.c_uint64, _i64, _i64, _i64]),
     "spamm_gen_uniform_alg": (_i, [_vp, C.c_uint64, _i64, _i64, _i64]),
     "spamm_gen_uniform": (_i, [_vp, C.c_uint64, _i64, _i64, _i64]),
@@ -108,8 +109,11 @@ def load() -> C.CDLL:
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if not path.exists():
-        path = _build.build_library()
+    try:
+        path = _build.build_library()      # returns at once when the library is newer than every source and header
+    except _build.NvccMissing:
+        if not path.exists():              # no compiler here: a library that travelled with the tree is used as it is
+            raise
     lib = C.CDLL(str(path))
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol

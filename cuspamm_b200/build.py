@@ -26,10 +26,14 @@ NVCC_FLAGS = [
 ]
 
 
+class NvccMissing(RuntimeError):
+    pass
+
+
 def _nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
-        raise RuntimeError("nvcc not found; libspamm.so cannot be built")
+        raise NvccMissing("nvcc not found; libspamm.so cannot be built")
     return exe
 
 
@@ -45,6 +49,7 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     srcs = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
     if not force and not _stale(LIB_PATH, list(srcs) + HEADERS):
         return LIB_PATH
+    _nvcc()
     build_dir = PKG_DIR / "build"
     build_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
@@ -74,6 +79,28 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     return LIB_PATH
 
 
+GEN_LIB_PATH = PKG_DIR / "libspamm_gen.so"
+
+
+def build_generators(force: bool = False) -> Path:
+    """Builds the host-side input generators alone (g++, no CUDA) into libspamm_gen.so: what a process that only
+    needs input matrices loads, e.g. the benchmark's CPU arm, which must not map the GPU library."""
+    src = CSRC / "generators.cpp"
+    header = PKG_DIR.parent / "include" / "spamm.h"
+    if not force and not _stale(GEN_LIB_PATH, [src, header]):
+        return GEN_LIB_PATH
+    gxx = shutil.which("g++")
+    if not gxx:
+        if GEN_LIB_PATH.exists():
+            return GEN_LIB_PATH
+        raise RuntimeError("g++ not found; libspamm_gen.so cannot be built")
+    cmd = [gxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", str(src), "-o", str(GEN_LIB_PATH)]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"generator build failed:\n{r.stdout}")
+    return GEN_LIB_PATH
+
+
 def build_driver(verbose: bool = False) -> Path:
     """Builds the command-line driver `spamm_main` (same shape as the reference's `main`) against libspamm.so."""
     build_library()
@@ -94,4 +121,5 @@ def build_driver(verbose: bool = False) -> Path:
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
     print(path)
+    print(build_generators(force="--force" in sys.argv))
     print(build_driver(verbose=True))

@@ -62,8 +62,8 @@ int norm_pack_pair_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda
 int build_lists_launch(const float *d_norm_a, const float *d_norm_b, int row_tiles, int k_tiles, int n_tiles, float tau,
                        void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts, int32_t *d_counts,
                        uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list, int32_t *d_busy_list,
-                       spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes, const PeerWait *wait,
-                       cudaStream_t stream);
+                       spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes, int keep_scalars,
+                       const PeerWait *wait, cudaStream_t stream);
 int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,
                      const uint32_t *d_tile_list, spamm_list_scalars *d_scalars, void *d_half_a, void *d_half_b,
                      void *d_low_a, void *d_low_b, bool reset_queues, cudaStream_t stream);
@@ -74,6 +74,9 @@ int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint
 // `mode` of gated_multiply_launch, a sum of:
 constexpr int GM_C_ZEROED = 1;      // C was cleared beforehand (or holds a partial result): macro tiles without steps are left alone
 constexpr int GM_ACCUMULATE = 2;    // the products are added to what C holds instead of replacing it
+constexpr int GM_LOW_OPERAND = 4;   // with GM_ACCUMULATE: one operand is a scaled low part, the sum is scaled back first
+// Split precision stores the low part of every element multiplied by this power of two (see pack_half.cu).
+constexpr float SPLIT_LOW_SCALE = 2048.0f;
 
 int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const int32_t *d_step_counts,
                                spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,

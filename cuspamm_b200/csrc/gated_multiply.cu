@@ -24,6 +24,8 @@
 // beforehand, or holds a partial result), and the products can be added to C instead of replacing it (the second and
 // third pass of the split-precision mode).  Every wait on an mbarrier is bounded in time; when one runs out the
 // block sets the error word, drains its copies and multiplies, frees its tensor memory and returns.
+#include <cstddef>
+
 #include "tc_utils.cuh"
 
 namespace spamm {
@@ -99,6 +101,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
 {
     const bool c_zeroed = (mode & GM_C_ZEROED) != 0;        // leave macro tiles without steps alone
     const bool accumulate = (mode & GM_ACCUMULATE) != 0;    // add to C
+    const float acc_scale = (mode & GM_LOW_OPERAND) ? 1.0f / SPLIT_LOW_SCALE : 1.0f;
     extern __shared__ uint8_t smem_raw[];
     // stage data first (128-byte aligned), control block after it
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -508,7 +511,7 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                 tmem_wait_ld();
                 tmem_st32_zero(taddr);
                 if (row_ok && mj * MT_C + cc < n_tiles)
-                    store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane, accumulate);
+                    store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane, accumulate, acc_scale);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -544,7 +547,9 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
 {
     using namespace spamm;
     // adding to C only makes sense where C is not overwritten with zeros, and never through the paired kernel
-    if (mode < 0 || mode > (GM_C_ZEROED | GM_ACCUMULATE) || ((mode & GM_ACCUMULATE) && (!(mode & GM_C_ZEROED) || try_pairs)))
+    if (mode < 0 || mode > (GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND) ||
+        ((mode & GM_ACCUMULATE) && (!(mode & GM_C_ZEROED) || try_pairs)) ||
+        ((mode & GM_LOW_OPERAND) && !(mode & GM_ACCUMULATE)))
         return SPAMM_ERR_INVALID;
     if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
         k_tiles < 0 || n_tiles < 0 || ldc < (int64_t)n_tiles * TILE || (ldc & 3) ||
@@ -570,8 +575,11 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
         sm_count_of[dev] = sms;
     }
     const int sm_count = sm_count_of[dev];
-    // the two work counters start from zero at every launch (unless the packing kernel just reset them)
-    if (reset_queues) SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 2 * sizeof(unsigned int), stream));
+    // the two work counters and the count of macro tiles the two-SM kernel wrote start from zero at every launch
+    // (unless the packing kernel just reset them): a second multiply over the same lists must not see the first one's
+    static_assert(offsetof(spamm_list_scalars, pair_done) == offsetof(spamm_list_scalars, queue_busy) + 8,
+                  "queue_busy, queue_all, pair_done are cleared as one block");
+    if (reset_queues) SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 3 * sizeof(unsigned int), stream));
     // dense macro tiles with a dense vertical neighbour go to pairs of SMs first (a no-op below half dense);
     // a caller that knows the lists are sparse can save the launch
     if (try_pairs) {

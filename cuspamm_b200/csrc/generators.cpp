@@ -77,6 +77,15 @@ int spamm_gen_decay_alg(float *out, float c, float v, int64_t row_begin, int64_t
     return SPAMM_OK;
 }
 
+int spamm_gen_ones(float *out, int64_t row_begin, int64_t rows, int64_t cols)
+{
+    if (bad(out, row_begin, rows, cols)) return SPAMM_ERR_INVALID;
+    parallel_rows(rows, [=](int64_t r) {
+        for (int64_t j = 0; j < cols; j++) out[r * cols + j] = 1.0f;
+    });
+    return SPAMM_OK;
+}
+
 int spamm_gen_signed_exp(float *out, double lambda, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols)
 {
     if (bad(out, row_begin, rows, cols)) return SPAMM_ERR_INVALID;

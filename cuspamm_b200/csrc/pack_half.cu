@@ -15,8 +15,14 @@
 
 namespace spamm {
 
-// the part of x that its half rounding leaves over (exact in float; rounded to half once more when stored)
-__device__ __forceinline__ float half_residual(float x) { return x - __half2float(__float2half_rn(x)); }
+// The part of x that its half rounding leaves over (exact in float), scaled by 2^11 before it is itself rounded to
+// half: the residual is at most half a unit in the last place of the high part, i.e. 2^-11 of it, so the scaled value
+// has the magnitude of the high part (never above 2^15) and keeps its bits where the unscaled one would fall into
+// half's subnormal range (inputs below 1e-4) or vanish (below 6e-8).  The multiply's adding passes scale back.
+__device__ __forceinline__ float half_residual(float x)
+{
+    return (x - __half2float(__float2half_rn(x))) * SPLIT_LOW_SCALE;
+}
 
 __device__ __forceinline__ uint4 pack8(const float *f)
 {
@@ -40,8 +46,8 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k
 {
     // low_a / low_b (both or neither): second set of packed tiles holding half(x - half(x)), same layout and
     // slab order, for the split-precision mode
-    // optional: the multiply kernel (next on the stream) starts its two work counters from zero
-    if (reset_queues && blockIdx.x == 0 && threadIdx.x < 2) (&sc->queue_busy)[threadIdx.x] = 0u;
+    // optional: the multiply kernel (next on the stream) starts its three work counters from zero
+    if (reset_queues && blockIdx.x == 0 && threadIdx.x < 3) (&sc->queue_busy)[threadIdx.x] = 0u;   // queue_busy, queue_all, pair_done
     __shared__ float tr[8][TILE][TILE + 1];
     __shared__ unsigned int blk_cnt[2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

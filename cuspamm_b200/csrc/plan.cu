@@ -1,6 +1,7 @@
 // Host side of the C ABI: the plan object that replaces the reference's `main` (cuSpAMM.cu:395-556) --
 // configuration, per-device buffers, the timed loop body and its event timing.
 #include <cmath>
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -34,7 +35,8 @@ constexpr size_t CHUNK_TARGET_BYTES = size_t(64) << 20;    // rows of A copied p
 using namespace spamm;
 
 struct spamm_plan {
-    int M = 0, K = 0, N = 0;
+    int M = 0, K = 0, N = 0;            // padded to multiples of 32 (main.h:54-56): the sizes every kernel works on
+    int in_M = 0, in_K = 0, in_N = 0;   // the caller's sizes: leading dimensions and extents of the host matrices
     int row_begin = 0, row_tiles = 0;   // in tiles
     int k_tiles = 0, n_tiles = 0, mi_n = 0, mj_n = 0;
     int device = 0;
@@ -91,6 +93,14 @@ struct spamm_plan {
     int64_t launches = 0;
 
     DeviceScalars *scalars() const { return reinterpret_cast<DeviceScalars *>(d_cleared); }
+    // rows of the caller's A (and C) that fall into this plan's block: the last block may end inside the padding
+    int rows_in() const
+    {
+        const int64_t left = (int64_t)in_M - (int64_t)row_begin * TILE;
+        const int64_t mine = (int64_t)row_tiles * TILE;
+        return (int)(left < 0 ? 0 : (left < mine ? left : mine));
+    }
+    bool padded() const { return in_M != M || in_K != K || in_N != N; }
     uint8_t *need_a() const { return d_cleared + need_a_off; }
     uint8_t *need_b() const { return d_cleared + need_b_off; }
     size_t bytes_a() const { return sizeof(float) * (size_t)row_tiles * TILE * K; }
@@ -138,13 +148,44 @@ int dev_alloc(T **p, size_t bytes)
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// rows x cols floats between a host matrix (leading dimension h_ld) and a device matrix (leading dimension d_ld);
+// one flat copy when both are packed the same way
+int copy_matrix(float *dst, size_t dst_ld, const float *src, size_t src_ld, size_t rows, size_t cols,
+                cudaMemcpyKind kind, cudaStream_t stream)
+{
+    if (rows == 0 || cols == 0) return SPAMM_OK;
+    if (dst_ld == cols && src_ld == cols)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(dst, src, sizeof(float) * rows * cols, kind, stream));
+    else
+        SPAMM_CUDA_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * dst_ld, src, sizeof(float) * src_ld, sizeof(float) * cols,
+                                         rows, kind, stream));
+    return SPAMM_OK;
+}
+
+// Zeroes the counters and need flags the list builder starts from, except the error and overflow words of every set
+// of counters: those stay until read_scalars has shown them to the host.
+int clear_list_state(spamm_plan *p, cudaStream_t stream)
+{
+    const size_t head = sizeof(DeviceScalars) * MAX_CHUNKS;
+    SPAMM_CUDA_TRY(cudaMemset2DAsync(p->d_cleared, sizeof(DeviceScalars), 0, offsetof(DeviceScalars, overflow),
+                                     MAX_CHUNKS, stream));
+    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared + head, 0, p->cleared_bytes - head, stream));
+    return SPAMM_OK;
+}
+
 int read_scalars(spamm_plan *p)
 {
-    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_scalars, p->scalars(), sizeof(DeviceScalars) * p->active_scalars,
+    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_scalars, p->scalars(), sizeof(DeviceScalars) * MAX_CHUNKS,
                                    cudaMemcpyDeviceToHost, p->stream));
-    if (p->peer_world > 1)
+    // the error and overflow words are sticky on the device (a list build does not clear them, so a failure in an
+    // earlier step of a queue of steps is still there); now that the host has them, they start afresh
+    SPAMM_CUDA_TRY(cudaMemset2DAsync(&p->scalars()->overflow, sizeof(DeviceScalars), 0, 2 * sizeof(int32_t), MAX_CHUNKS,
+                                     p->stream));
+    if (p->peer_world > 1) {
         SPAMM_CUDA_TRY(cudaMemcpyAsync(p->h_peer_error, p->d_peer_error, sizeof(int), cudaMemcpyDeviceToHost,
                                        p->stream));
+        SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_peer_error, 0, sizeof(int), p->stream));
+    }
     SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
     // remember whether these lists were mostly dense: the next multiply launches the paired kernel only then
     // (a wrong guess costs speed, never correctness: the one-SM kernel is told whether the paired one ran)
@@ -170,7 +211,7 @@ int read_scalars(spamm_plan *p)
 int status_from_scalars(const spamm_plan *p)
 {
     if (p->peer_world > 1 && *p->h_peer_error) return SPAMM_ERR_DEVICE_WAIT;
-    for (int c = 0; c < p->active_scalars; c++) {
+    for (int c = 0; c < MAX_CHUNKS; c++) {     // every set: an earlier call may have used more sets than the last
         if (p->h_scalars[c].error) return SPAMM_ERR_DEVICE_WAIT;
         if (p->h_scalars[c].overflow) return SPAMM_ERR_OVERFLOW;
     }
@@ -217,10 +258,14 @@ int spamm_plan_set_precision(spamm_plan *p, int precision)
 {
     if (!p || (precision != SPAMM_PRECISION_HALF && precision != SPAMM_PRECISION_SPLIT)) return SPAMM_ERR_INVALID;
     DeviceGuard guard(p->device);
-    if (precision == SPAMM_PRECISION_SPLIT && !p->d_low_a) {
+    if (precision == SPAMM_PRECISION_SPLIT && (!p->d_low_a || !p->d_low_b)) {
         int st;
-        if ((st = dev_alloc(&p->d_low_a, p->bytes_half_a()))) return st;
-        if ((st = dev_alloc(&p->d_low_b, p->bytes_half_b()))) return st;
+        if (!p->d_low_a && (st = dev_alloc(&p->d_low_a, p->bytes_half_a()))) return st;
+        if (!p->d_low_b && (st = dev_alloc(&p->d_low_b, p->bytes_half_b()))) {
+            cudaFree(p->d_low_a);       // both or neither: a later call starts over
+            p->d_low_a = nullptr;
+            return st;
+        }
     }
     if (precision != p->precision) {
         p->have_pack = false;       // the packed tiles belong to the other mode
@@ -252,7 +297,14 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
 {
     if (!out) return SPAMM_ERR_INVALID;
     *out = nullptr;
-    if (M <= 0 || K <= 0 || N <= 0 || M % TILE || K % TILE || N % TILE) return SPAMM_ERR_INVALID;
+    if (M <= 0 || K <= 0 || N <= 0 || M > INT32_MAX - TILE || K > INT32_MAX - TILE || N > INT32_MAX - TILE)
+        return SPAMM_ERR_INVALID;
+    // sizes that are not multiples of 32 are padded with zeros on the device (the reference pads, main.h:54-56, and
+    // leaves the padding uninitialised, cuSpAMM.cu:410); zero tiles have norm 0 and zero rows add nothing
+    const int in_M = M, in_K = K, in_N = N;
+    M = (M + TILE - 1) / TILE * TILE;
+    K = (K + TILE - 1) / TILE * TILE;
+    N = (N + TILE - 1) / TILE * TILE;
     if (row_tile_begin < 0 || row_tile_count < 0 || row_tile_begin + (int64_t)row_tile_count > M / TILE)
         return SPAMM_ERR_INVALID;
     if (K / TILE > 65535) return SPAMM_ERR_UNSUPPORTED;
@@ -268,6 +320,7 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     spamm_plan *p = new (std::nothrow) spamm_plan();
     if (!p) return SPAMM_ERR_ALLOC;
     p->M = M; p->K = K; p->N = N;
+    p->in_M = in_M; p->in_K = in_K; p->in_N = in_N;
     p->row_begin = row_tile_begin; p->row_tiles = row_tile_count;
     p->k_tiles = K / TILE; p->n_tiles = N / TILE;
     p->mi_n = ceil_div(p->row_tiles, MT_R); p->mj_n = ceil_div(p->n_tiles, MT_C);
@@ -312,6 +365,11 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     if ((st = dev_alloc(&p->d_a, p->bytes_a()))) return fail(st);
     if ((st = dev_alloc(&p->d_b, p->bytes_b()))) return fail(st);
     if ((st = dev_alloc(&p->d_c, p->bytes_c()))) return fail(st);
+    if (p->padded()) {
+        // uploads write the caller's extent only: the padding is cleared once, here, and stays zero
+        if (cudaMemset(p->d_a, 0, p->bytes_a()) != cudaSuccess || cudaMemset(p->d_b, 0, p->bytes_b()) != cudaSuccess)
+            return fail(record_cuda_error(cudaGetLastError(), "cudaMemset(padding)"));
+    }
     if ((st = dev_alloc(&p->d_norm_a, p->bytes_norm_a()))) return fail(st);
     if ((st = dev_alloc(&p->d_norm_b_buf[0], p->bytes_norm_b()))) return fail(st);
     if ((st = dev_alloc(&p->d_norm_b_buf[1], p->bytes_norm_b()))) return fail(st);
@@ -355,7 +413,8 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     if (cudaMallocHost(reinterpret_cast<void **>(&p->h_cv), 16) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMallocHost"));
     memset(p->h_scalars, 0, sizeof(DeviceScalars) * MAX_CHUNKS);
-    if (cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream) != cudaSuccess ||
+    if (p->cleared_bytes < sizeof(DeviceScalars) * MAX_CHUNKS + 16 ||
+        cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream) != cudaSuccess ||
         cudaStreamSynchronize(p->stream) != cudaSuccess)
         return fail(record_cuda_error(cudaGetLastError(), "cudaMemsetAsync"));
     *out = p;
@@ -401,9 +460,12 @@ int spamm_upload(spamm_plan *p, const float *a_rows, const float *b)
 {
     if (!p) return SPAMM_ERR_INVALID;
     DeviceGuard guard(p->device);
-    if (a_rows && p->row_tiles)
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a, a_rows, p->bytes_a(), cudaMemcpyHostToDevice, p->stream));
-    if (b) SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream));
+    int st;
+    if (a_rows && (st = copy_matrix(p->d_a, p->K, a_rows, p->in_K, p->rows_in(), p->in_K, cudaMemcpyHostToDevice,
+                                    p->stream)))
+        return st;
+    if (b && (st = copy_matrix(p->d_b, p->N, b, p->in_N, p->in_K, p->in_N, cudaMemcpyHostToDevice, p->stream)))
+        return st;
     if (a_rows || b) p->have_norms = p->have_lists = p->have_pack = false;
     return SPAMM_OK;
 }
@@ -591,13 +653,14 @@ static int build_lists_impl(spamm_plan *p, float tau, bool whole_step)
         int st = build_lists_launch(p->d_norm_a, p->d_norm_b, p->row_tiles, p->k_tiles, p->n_tiles, tau,
                                     p->d_list_scratch, p->d_steps, p->d_step_counts, p->d_counts, p->need_a(),
                                     p->need_b(), p->d_tile_list, p->d_busy, p->scalars(), p->d_cleared,
-                                    p->cleared_bytes, p->peer_wait_pending ? &wait : nullptr, p->stream);
+                                    p->cleared_bytes, MAX_CHUNKS, p->peer_wait_pending ? &wait : nullptr, p->stream);
         p->peer_wait_pending = false;
         if (st) return st;
         p->launches += 2;
         p->queues_clean = true;     // the clear covers the multiply's two work counters
     } else {
-        SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
+        int st = clear_list_state(p, p->stream);
+        if (st) return st;
     }
     p->have_lists = true;
     p->have_pack = false;
@@ -644,7 +707,7 @@ int spamm_gated_multiply(spamm_plan *p)
                 st = gated_multiply_launch(pass == 0 ? p->d_half_a : p->d_low_a, pass == 0 ? p->d_low_b : p->d_half_b,
                                            p->d_steps, p->d_step_counts, p->d_order, p->d_busy, p->scalars(),
                                            p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, true, false,
-                                           GM_C_ZEROED | GM_ACCUMULATE, p->stream);
+                                           GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, p->stream);
                 if (st) return st;
                 p->launches++;
             }
@@ -675,8 +738,8 @@ int spamm_download_c(spamm_plan *p, float *c_rows)
 {
     if (!p || !c_rows) return SPAMM_ERR_INVALID;
     DeviceGuard guard(p->device);
-    if (p->row_tiles)
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows, p->d_c, p->bytes_c(), cudaMemcpyDeviceToHost, p->stream));
+    int st = copy_matrix(c_rows, p->in_N, p->d_c, p->N, p->rows_in(), p->in_N, cudaMemcpyDeviceToHost, p->stream);
+    if (st) return st;
     SPAMM_CUDA_TRY(cudaStreamSynchronize(p->stream));
     return SPAMM_OK;
 }
@@ -796,7 +859,7 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
                                         p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0, d_order,
                                         p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
                                         p->d_c + (size_t)t0 * TILE * p->N, p->N, true, false,
-                                        GM_C_ZEROED | GM_ACCUMULATE, stream)))
+                                        GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, stream)))
             return st;
         p->launches++;
     }
@@ -814,8 +877,8 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
         if ((st = spamm_upload(p, a_rows, b))) return st;
         if ((st = run_with_events(p, tau))) return st;
-        if (p->row_tiles)
-            SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows, p->d_c, p->bytes_c(), cudaMemcpyDeviceToHost, p->stream));
+        if ((st = copy_matrix(c_rows, p->in_N, p->d_c, p->N, p->rows_in(), p->in_N, cudaMemcpyDeviceToHost, p->stream)))
+            return st;
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev[6], p->stream));
         if ((st = read_scalars(p))) return st;
         if (stats) {
@@ -834,20 +897,31 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
     // B goes up first (every C row needs all of it); then the rows of A go up chunk by chunk, each chunk runs the
     // whole path on the main stream, and its rows of C go down on a second stream while the next chunk goes up.
     p->packed_all = false;
+    if (p->c_zero_pending) {
+        // an early clearing of C announced for a step that never came: it must have ended before chunks write C
+        SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_zero[1], 0));
+        p->c_zero_pending = false;
+    }
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
-    SPAMM_CUDA_TRY(cudaMemsetAsync(p->d_cleared, 0, p->cleared_bytes, p->stream));
+    if ((st = clear_list_state(p, p->stream))) return st;
     // All uploads go back to back on their own stream (they start after everything already queued on the main
     // stream, which may still read the old matrices); the main stream waits for B, then for each chunk of rows.
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[MAX_CHUNKS + 1], p->stream));
     SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_h2d, p->ev_up[MAX_CHUNKS + 1], 0));
-    SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_b, b, p->bytes_b(), cudaMemcpyHostToDevice, p->stream_h2d));
+    if ((st = copy_matrix(p->d_b, p->N, b, p->in_N, p->in_K, p->in_N, cudaMemcpyHostToDevice, p->stream_h2d))) return st;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[MAX_CHUNKS], p->stream_h2d));
+    const int rows_in = p->rows_in();
+    // rows of the caller's matrices inside a chunk of tile rows (the last chunk may reach into the padding)
+    auto rows_of = [&](int t0, int tiles) {
+        const int lo = t0 * TILE, hi = (t0 + tiles) * TILE;
+        return (size_t)(rows_in <= lo ? 0 : (rows_in < hi ? rows_in : hi) - lo);
+    };
     for (int c = 0; c < p->n_chunks; c++) {
         const int t0 = c * p->chunk_tiles;
         const int tiles = (c == p->n_chunks - 1) ? p->row_tiles - t0 : p->chunk_tiles;
-        const size_t a_off = (size_t)t0 * TILE * p->K;
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(p->d_a + a_off, a_rows + a_off, sizeof(float) * (size_t)tiles * TILE * p->K,
-                                       cudaMemcpyHostToDevice, p->stream_h2d));
+        if ((st = copy_matrix(p->d_a + (size_t)t0 * TILE * p->K, p->K, a_rows + (size_t)t0 * TILE * p->in_K, p->in_K,
+                              rows_of(t0, tiles), p->in_K, cudaMemcpyHostToDevice, p->stream_h2d)))
+            return st;
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[c], p->stream_h2d));
     }
     SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_up[MAX_CHUNKS], 0));
@@ -865,8 +939,9 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
             return st;
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev_chunk[c], p->stream));
         SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_d2h, p->ev_chunk[c], 0));
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(c_rows + c_off, p->d_c + c_off, sizeof(float) * (size_t)tiles * TILE * p->N,
-                                       cudaMemcpyDeviceToHost, p->stream_d2h));
+        if ((st = copy_matrix(c_rows + (size_t)t0 * TILE * p->in_N, p->in_N, p->d_c + c_off, p->N, rows_of(t0, tiles),
+                              p->in_N, cudaMemcpyDeviceToHost, p->stream_d2h)))
+            return st;
     }
     // the main stream ends when the last rows of C have arrived
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[7], p->stream_d2h));
@@ -1095,9 +1170,9 @@ int spamm_stream(spamm_plan *p, void **stream)
 int spamm_plan_dims(spamm_plan *p, int *M, int *K, int *N, int *row_tile_begin, int *row_tile_count)
 {
     if (!p) return SPAMM_ERR_INVALID;
-    if (M) *M = p->M;
-    if (K) *K = p->K;
-    if (N) *N = p->N;
+    if (M) *M = p->in_M;
+    if (K) *K = p->in_K;
+    if (N) *N = p->in_N;
     if (row_tile_begin) *row_tile_begin = p->row_begin;
     if (row_tile_count) *row_tile_count = p->row_tiles;
     return SPAMM_OK;

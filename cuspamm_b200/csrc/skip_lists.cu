@@ -19,6 +19,8 @@
 //
 // By-products for the next two kernels: the list of distinct tiles of A and of B that some step names (what has to
 // be converted to half) and the list of macro tiles that have at least one step (scheduled first by the multiply).
+#include <cstddef>
+
 #include "common.cuh"
 
 namespace spamm {
@@ -53,14 +55,29 @@ __global__ void peer_wait_selftest_kernel(PeerWait wait) { peer_wait(wait); }
 __global__ void __launch_bounds__(256)
 chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
                  int n_tiles, float *__restrict__ amax, float *__restrict__ bmax, uint4 *__restrict__ clear,
-                 size_t clear_vecs, PeerWait wait)
+                 size_t clear_vecs, int keep_scalars, PeerWait wait)
 {
     // optional: B's norm map is assembled by the other GPUs writing their shares into it; wait (at most 2 s) until
     // every sender's flag has reached this step's number
     peer_wait(wait);
-    // optional: zero the counters and need flags the list builder (the next kernel) starts from
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < clear_vecs; i += (size_t)gridDim.x * blockDim.x)
-        clear[i] = make_uint4(0u, 0u, 0u, 0u);
+    // optional: zero the counters and need flags the list builder (the next kernel) starts from.  The region begins
+    // with `keep_scalars` sets of counters whose error and overflow words survive: a wait that ran out in an earlier
+    // step must still be there when the host next looks (spamm_sync clears the two after reporting them).
+    const size_t head_bytes = (size_t)keep_scalars * sizeof(spamm_list_scalars);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < clear_vecs; i += (size_t)gridDim.x * blockDim.x) {
+        if (i * 16 >= head_bytes) {
+            clear[i] = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+            uint32_t *w = reinterpret_cast<uint32_t *>(clear + i);
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const size_t off = (i * 16 + 4 * x) % sizeof(spamm_list_scalars);
+                if (i * 16 + 4 * x >= head_bytes ||
+                    (off != offsetof(spamm_list_scalars, overflow) && off != offsetof(spamm_list_scalars, error)))
+                    w[x] = 0u;
+            }
+        }
+    }
     const int lane = threadIdx.x & 31;
     const int mi_n = (row_tiles + MT_R - 1) / MT_R;
     const int mj_n = (n_tiles + MT_C - 1) / MT_C;
@@ -304,7 +321,7 @@ int spamm::build_lists_launch(const float *d_norm_a, const float *d_norm_b, int 
                               float tau, void *d_scratch, uint32_t *d_steps, int32_t *d_step_counts,
                               int32_t *d_counts, uint8_t *d_need_a, uint8_t *d_need_b, uint32_t *d_tile_list,
                               int32_t *d_busy_list, spamm_list_scalars *d_scalars, void *d_clear, size_t clear_bytes,
-                              const PeerWait *wait, cudaStream_t stream)
+                              int keep_scalars, const PeerWait *wait, cudaStream_t stream)
 {
     using namespace spamm;
     if (!d_norm_a || !d_norm_b || !d_scratch || !d_steps || !d_step_counts || !d_counts || !d_need_a || !d_need_b ||
@@ -328,7 +345,7 @@ int spamm::build_lists_launch(const float *d_norm_a, const float *d_norm_b, int 
     if (wait) w = *wait;
     chunk_max_kernel<<<(unsigned)cm_blocks, 256, 0, stream>>>(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, amax,
                                                              bmax, static_cast<uint4 *>(d_clear),
-                                                             d_clear ? clear_bytes / 16 : 0, w);
+                                                             d_clear ? clear_bytes / 16 : 0, keep_scalars, w);
     build_lists_kernel<<<(unsigned)blocks, 128, 0, stream>>>(
         d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, amax, bmax, d_steps, d_step_counts, d_counts, d_need_a,
         d_need_b, d_tile_list, d_busy_list, d_scalars);
@@ -344,5 +361,5 @@ extern "C" int spamm_build_lists_dev(const float *d_norm_a, const float *d_norm_
 {
     return spamm::build_lists_launch(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles, tau, d_scratch, d_steps,
                                      d_step_counts, d_counts, d_need_a, d_need_b, d_tile_list, d_busy_list, d_scalars,
-                                     nullptr, 0, nullptr, (cudaStream_t)stream);
+                                     nullptr, 0, 0, nullptr, (cudaStream_t)stream);
 }

@@ -3,7 +3,7 @@
 // time.  What para.h fixes at compile time is a command-line option here:
 //
 //   spamm_main [--n N | --m M --k K --nn N] [--devices D] [--tau T] [--iters I] [--warmup W]
-//              [--matrix alg|exp|sexp|ualg|uniform] [--tune RATE] [--float]
+//              [--matrix alg|exp|ones|sexp|ualg|uniform] [--tune RATE] [--float]
 //
 // --float is the counterpart of building the reference with USINGHALF 0 (para.h): float-level accuracy, here through
 // the split-precision mode on the tensor cores.
@@ -11,7 +11,9 @@
 // Defaults are the reference's: 2048^3, one device, tau = 1.548969, algebraic decay c=v=0.1, 10 iterations of which
 // the first 5 are warm-up (para.h:1-14).  Differences: the mean is the true mean over the timed iterations (the
 // reference divides 4 samples by 5, cuSpAMM.cu:545,549), every device is synchronised before the clock stops
-// (cuSpAMM.cu:539 waits for one), and inputs are float (the conversion to half happens on the GPU).
+// (cuSpAMM.cu:539 waits for one), inputs are float (the conversion to half happens on the GPU), and sizes that are
+// not multiples of 32 are padded with zeros by the library (the reference extends its generated pattern into the
+// padding or leaves it uninitialised, cuSpAMM.cu:410,425-430).
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -63,18 +65,19 @@ int main(int argc, char **argv)
         return 1;
     }
     float *h_A = nullptr, *h_B = nullptr, *h_C = nullptr;
-    if (cudaMallocHost(&h_A, sizeof(float) * (size_t)Mp * Kp) != cudaSuccess ||
-        cudaMallocHost(&h_B, sizeof(float) * (size_t)Kp * Np) != cudaSuccess ||
-        cudaMallocHost(&h_C, sizeof(float) * (size_t)Mp * Np) != cudaSuccess) {
+    if (cudaMallocHost(&h_A, sizeof(float) * (size_t)M * K) != cudaSuccess ||
+        cudaMallocHost(&h_B, sizeof(float) * (size_t)K * N) != cudaSuccess ||
+        cudaMallocHost(&h_C, sizeof(float) * (size_t)M * N) != cudaSuccess) {
         fprintf(stderr, "host allocation failed\n");
         return 1;
     }
     int st = 0;
-    if (matrix == "alg") { st |= spamm_gen_decay_alg(h_A, 0.1f, 0.1f, 0, Mp, Kp); st |= spamm_gen_decay_alg(h_B, 0.1f, 0.1f, 0, Kp, Np); }
-    else if (matrix == "exp") { st |= spamm_gen_decay_exp(h_A, 1.0f, 0.1f, 0, Mp, Kp); st |= spamm_gen_decay_exp(h_B, 1.0f, 0.1f, 0, Kp, Np); }
-    else if (matrix == "sexp") { st |= spamm_gen_signed_exp(h_A, 0.1, 1, 0, Mp, Kp); st |= spamm_gen_signed_exp(h_B, 0.1, 2, 0, Kp, Np); }
-    else if (matrix == "ualg") { st |= spamm_gen_uniform_alg(h_A, 3, 0, Mp, Kp); st |= spamm_gen_uniform_alg(h_B, 4, 0, Kp, Np); }
-    else if (matrix == "uniform") { st |= spamm_gen_uniform(h_A, 5, 0, Mp, Kp); st |= spamm_gen_uniform(h_B, 6, 0, Kp, Np); }
+    if (matrix == "alg") { st |= spamm_gen_decay_alg(h_A, 0.1f, 0.1f, 0, M, K); st |= spamm_gen_decay_alg(h_B, 0.1f, 0.1f, 0, K, N); }
+    else if (matrix == "ones") { st |= spamm_gen_ones(h_A, 0, M, K); st |= spamm_gen_ones(h_B, 0, K, N); }   // MATRIXNOR
+    else if (matrix == "exp") { st |= spamm_gen_decay_exp(h_A, 1.0f, 0.1f, 0, M, K); st |= spamm_gen_decay_exp(h_B, 1.0f, 0.1f, 0, K, N); }
+    else if (matrix == "sexp") { st |= spamm_gen_signed_exp(h_A, 0.1, 1, 0, M, K); st |= spamm_gen_signed_exp(h_B, 0.1, 2, 0, K, N); }
+    else if (matrix == "ualg") { st |= spamm_gen_uniform_alg(h_A, 3, 0, M, K); st |= spamm_gen_uniform_alg(h_B, 4, 0, K, N); }
+    else if (matrix == "uniform") { st |= spamm_gen_uniform(h_A, 5, 0, M, K); st |= spamm_gen_uniform(h_B, 6, 0, K, N); }
     else { fprintf(stderr, "unknown matrix kind %s\n", matrix.c_str()); return 2; }
     if (st) return fail("generator", st);
 
@@ -84,10 +87,10 @@ int main(int argc, char **argv)
         begin[d] = b;
         count[d] = (d == devices - 1) ? row_tiles - b : row_tiles / devices;
         b += count[d];
-        if ((st = spamm_plan_create(&plan[d], Mp, Kp, Np, begin[d], count[d], d))) return fail("spamm_plan_create", st);
+        if ((st = spamm_plan_create(&plan[d], M, K, N, begin[d], count[d], d))) return fail("spamm_plan_create", st);
         if (split && (st = spamm_plan_set_precision(plan[d], SPAMM_PRECISION_SPLIT)))
             return fail("spamm_plan_set_precision", st);
-        if ((st = spamm_upload(plan[d], h_A + (size_t)begin[d] * 32 * Kp, h_B))) return fail("spamm_upload", st);
+        if ((st = spamm_upload(plan[d], h_A + (size_t)begin[d] * 32 * K, h_B))) return fail("spamm_upload", st);
     }
     float norm = (float)tau;
     if (tune > 0) {                                     // TUNINGFLAG, main.h:35-38, cuSpAMM.cu:513-515
@@ -111,7 +114,7 @@ int main(int argc, char **argv)
         int64_t s = 0;
         if ((st = spamm_get_counts(plan[d], nullptr, &s))) return fail("spamm_get_counts", st);
         survivors += s;
-        if ((st = spamm_download_c(plan[d], h_C + (size_t)begin[d] * 32 * Np))) return fail("spamm_download_c", st);
+        if ((st = spamm_download_c(plan[d], h_C + (size_t)begin[d] * 32 * N))) return fail("spamm_download_c", st);
     }
     const double t = sum / (iters - warmup);
     const double total = (double)(Mp / 32) * (Kp / 32) * (Np / 32);

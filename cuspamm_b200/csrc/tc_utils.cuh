@@ -139,9 +139,9 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 constexpr int EPI_ROW_BYTES = 144;
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;          // 4608 bytes per epilogue warp
 
-// With `add` the block is added to what C holds (float addition, C's value first).
+// With `add` the block, times `scale` (a power of two), is added to what C holds.
 __device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const uint32_t *v, float *c_block,
-                                                      int64_t ldc, int lane, bool add = false)
+                                                      int64_t ldc, int lane, bool add = false, float scale = 1.0f)
 {
     uint4 *mine = reinterpret_cast<uint4 *>(warp_tile + lane * EPI_ROW_BYTES);
 #pragma unroll
@@ -155,10 +155,10 @@ __device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const 
         float4 *dst = reinterpret_cast<float4 *>(c_block + (int64_t)r * ldc + part * 4);
         if (add) {
             const float4 old = *dst;
-            o.x = old.x + o.x;
-            o.y = old.y + o.y;
-            o.z = old.z + o.z;
-            o.w = old.w + o.w;
+            o.x = __fmaf_rn(o.x, scale, old.x);
+            o.y = __fmaf_rn(o.y, scale, old.y);
+            o.z = __fmaf_rn(o.z, scale, old.z);
+            o.w = __fmaf_rn(o.w, scale, old.w);
         }
         __stcs(dst, o);
     }

@@ -45,7 +45,8 @@ def _host_ptr(x, nbytes: Optional[int] = None) -> int:
 
 def pad_to_tiles(x: np.ndarray) -> np.ndarray:
     """Zero-pads a float32 matrix to multiples of 32 in both dimensions, the reference's padded sizes
-    (main.h:54-56; the reference leaves the padding uninitialised, zeros make it harmless)."""
+    (main.h:54-56; the reference leaves the padding uninitialised, zeros make it harmless).  The library pads by
+    itself on the GPU; this helper only serves comparisons on the host."""
     r, c = x.shape
     R, Cc = -(-r // TILE) * TILE, -(-c // TILE) * TILE
     if (R, Cc) == (r, c) and x.dtype == np.float32 and x.flags["C_CONTIGUOUS"]:
@@ -140,8 +141,9 @@ class SpammPlan:
                  device: int = 0):
         self._lib = _lib.load()
         if row_tile_count is None:
-            row_tile_count = M // TILE - row_tile_begin
-        self.M, self.K, self.N = M, K, N
+            row_tile_count = -(-M // TILE) - row_tile_begin
+        self.M, self.K, self.N = M, K, N                       # the caller's sizes; the library pads to 32 on the GPU
+        self.Mp, self.Kp, self.Np = (-(-x // TILE) * TILE for x in (M, K, N))
         self.row_tile_begin, self.row_tile_count = row_tile_begin, row_tile_count
         self.device = device
         self._h = C.c_void_p()
@@ -169,15 +171,16 @@ class SpammPlan:
     # ---- shapes
     @property
     def rows(self) -> int:
-        return self.row_tile_count * TILE
+        """Rows of the caller's A and C inside this plan's block (the last block may end inside the padding)."""
+        return max(0, min(self.row_tile_count * TILE, self.M - self.row_tile_begin * TILE))
 
     @property
     def k_tiles(self) -> int:
-        return self.K // TILE
+        return self.Kp // TILE
 
     @property
     def n_tiles(self) -> int:
-        return self.N // TILE
+        return self.Np // TILE
 
     def set_chunk_tiles(self, tiles: int) -> None:
         """Tile rows per chunk of the pipelined `multiply` (multiple of 4)."""
@@ -339,9 +342,9 @@ class SpammPlan:
 
         ptr, nbytes = self.buffer(which)
         shapes = {
-            BUF_A: ((self.rows, self.K), "<f4"),
-            BUF_B: ((self.K, self.N), "<f4"),
-            BUF_C: ((self.rows, self.N), "<f4"),
+            BUF_A: ((self.row_tile_count * TILE, self.Kp), "<f4"),
+            BUF_B: ((self.Kp, self.Np), "<f4"),
+            BUF_C: ((self.row_tile_count * TILE, self.Np), "<f4"),
             BUF_NORM_A: ((self.row_tile_count, self.k_tiles), "<f4"),
             BUF_NORM_B: ((self.k_tiles, self.n_tiles), "<f4"),
             BUF_COUNTS: ((self.row_tile_count, self.n_tiles), "<i4"),
@@ -383,11 +386,11 @@ class ShardedSpamm:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.M, self.K, self.N = M, K, N
         if blocks is None:
-            blocks = row_blocks(M // TILE, self.world)          # the reference's even split
+            blocks = row_blocks(-(-M // TILE), self.world)      # the reference's even split
         else:                                                   # e.g. from balanced_row_blocks
             blocks = [(int(b), int(c)) for b, c in blocks]
             ends = [b + c for b, c in blocks]
-            if (len(blocks) != self.world or blocks[0][0] != 0 or ends[-1] != M // TILE
+            if (len(blocks) != self.world or blocks[0][0] != 0 or ends[-1] != -(-M // TILE)
                     or any(c < 0 for _, c in blocks) or any(blocks[i + 1][0] != ends[i] for i in range(self.world - 1))):
                 raise ValueError("blocks must tile the C tile rows contiguously, one block per rank")
         self.blocks = blocks
@@ -396,14 +399,14 @@ class ShardedSpamm:
             dev = torch.cuda.current_device() if device is None else device
             plan_factory = lambda M, K, N, b, c: SpammPlan(M, K, N, b, c, device=dev)  # noqa: E731
         self.plan = plan_factory(M, K, N, self.row_tile_begin, self.row_tile_count)
-        k_tiles = K // TILE
+        k_tiles = -(-K // TILE)
         # equal shares of B's tile rows when they divide evenly, otherwise every rank computes the whole map
         self._share = (k_tiles // self.world) if (self.world > 1 and k_tiles % self.world == 0) else None
         self._nb = self._mine = self._stream = self._side = None
         self._nccl = False
         # peer-to-peer exchange of B's norm-map shares (no collective in the step) when the plan offers it
         self._push = False
-        if (exchange == "push" and self._share is not None and (self._share * (N // TILE)) % 4 == 0
+        if (exchange == "push" and self._share is not None and (self._share * -(-N // TILE)) % 4 == 0
                 and hasattr(self.plan, "peer_handles")
                 and self.world <= 8 and dist.get_backend(group) == "nccl"):
             mine = self.plan.peer_handles()
@@ -566,42 +569,6 @@ class ShardedSpamm:
             close()
 
 
-# ---- generators (host side) -------------------------------------------------------------------------------
-
-def _gen(fn_name: str, rows: int, cols: int, *args) -> np.ndarray:
-    lib = _lib.load()
-    out = np.empty((rows, cols), dtype=np.float32)
-    check(getattr(lib, fn_name)(out.ctypes.data, *args), fn_name)
-    return out
-
-
-def gen_decay_exp(c: float, v: float, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
-    """a_ij = c * v^|i-j| (getDecayMatrixExp, tool.cu:409-422)."""
-    return _gen("spamm_gen_decay_exp", rows, cols, c, v, row_begin, rows, cols)
-
-
-def gen_decay_alg(c: float, v: float, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
-    """a_ij = c / (|i-j|^v + 1) (getDecayMatrixAlg, tool.cu:426-436)."""
-    return _gen("spamm_gen_decay_alg", rows, cols, c, v, row_begin, rows, cols)
-
-
-def gen_signed_exp(lam: float, seed: int, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
-    """a_ij = s_ij * exp(-lam*|i-j|), s_ij = +-1 from a hash of (seed, i, j)."""
-    return _gen("spamm_gen_signed_exp", rows, cols, lam, seed, row_begin, rows, cols)
-
-
-def gen_uniform_alg(seed: int, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
-    """a_ij = u_ij / (|i-j|^2 + 1), u uniform in [-1, 1)."""
-    return _gen("spamm_gen_uniform_alg", rows, cols, seed, row_begin, rows, cols)
-
-
-def gen_uniform(seed: int, rows: int, cols: int, row_begin: int = 0) -> np.ndarray:
-    """a_ij uniform in [-1, 1)."""
-    return _gen("spamm_gen_uniform", rows, cols, seed, row_begin, rows, cols)
-
-
-def gen_lattice(L: int, seed: int, rows: Optional[int] = None, row_begin: int = 0) -> np.ndarray:
-    """Symmetric surrogate of a density matrix on an L^3 grid: a_ij = +-u * exp(-|r_i - r_j|), u in [0.5, 1)."""
-    n = L ** 3
-    rows = n - row_begin if rows is None else rows
-    return _gen("spamm_gen_lattice", rows, n, L, seed, row_begin, rows)
+# ---- generators (host side): csrc/generators.cpp through its own small library
+from .hostgen import (gen_decay_alg, gen_decay_exp, gen_lattice, gen_ones, gen_signed_exp, gen_uniform,  # noqa: E402,F401
+                      gen_uniform_alg)

@@ -9,8 +9,10 @@
  * reference lines it stands in for (paths inside the reference project).
  *
  * Conventions
- *   - all matrices are row-major float; M, K, N must be multiples of 32 (the reference pads to that,
- *     main.h:54-56; callers pad with zeros);
+ *   - all matrices are row-major float with no gaps between rows (leading dimension = number of columns).  M, K, N
+ *     need not be multiples of 32: the library pads them on the device, with zeros, to the next multiple, as the
+ *     reference pads its sizes (main.h:54-56; it leaves the padding uninitialised, cuSpAMM.cu:410).  Host matrices
+ *     keep the caller's sizes on the way in and out; norm maps, list lengths and device buffers have the padded ones;
  *   - a plan owns one GPU and one block of C tile rows [row_tile_begin, row_tile_begin+row_tile_count),
  *     which is the reference's per-device row split (cuSpAMM.cu:503,530 `main_row_offset`); one plan per
  *     process and GPU, a multi-GPU run is several plans;
@@ -36,7 +38,7 @@ extern "C" {
 
 typedef enum spamm_status {
     SPAMM_OK = 0,
-    SPAMM_ERR_INVALID = 1,      /* bad argument (null pointer, dimension not a multiple of 32, bad row block) */
+    SPAMM_ERR_INVALID = 1,      /* bad argument (null pointer, non-positive dimension, bad row block) */
     SPAMM_ERR_CUDA = 2,         /* a CUDA runtime call failed; see spamm_last_cuda_error */
     SPAMM_ERR_ALLOC = 3,        /* device or host allocation failed */
     SPAMM_ERR_DEVICE_WAIT = 4,  /* a bounded wait inside a kernel ran out; results are not valid */
@@ -75,12 +77,12 @@ typedef struct spamm_list_scalars {
     unsigned int busy_count;        /* entries of the list of macro tiles that have steps */
     unsigned int packed_a;          /* tiles of A converted by the packing kernel */
     unsigned int packed_b;          /* tiles of B converted by the packing kernel */
-    unsigned int queue_busy;        /* work counters of the multiply kernel; every multiply call resets the two */
+    unsigned int queue_busy;        /* work counters of the multiply kernels; every multiply call resets the three */
     unsigned int queue_all;
+    unsigned int pair_done;         /* macro tiles the two-SM multiply kernel took care of in this call */
     unsigned int dense_count;       /* macro tiles whose list has every k with every row and column (list builder) */
-    unsigned int pair_done;         /* macro tiles the paired (two-SM) multiply kernel took care of */
-    int32_t overflow;               /* non-zero: a step list did not fit */
-    int32_t error;                  /* non-zero: a bounded wait of the multiply kernel ran out (which one) */
+    int32_t overflow;               /* non-zero: a step list did not fit; kept until spamm_sync has reported it */
+    int32_t error;                  /* non-zero: a bounded wait of the multiply kernel ran out (which one); kept likewise */
 } spamm_list_scalars;
 
 /* Names for spamm_device_buffer. */
@@ -103,7 +105,8 @@ typedef enum spamm_buffer {
  * Replaces the compile-time configuration and per-device allocation of the reference:
  * inM/inK/inN (para.h:6-8), the row split over DEVICEDIM devices (para.h:9, cuSpAMM.cu:503,530) and
  * the cudaMallocManaged block (cuSpAMM.cu:433-451).  `device` is a CUDA ordinal.  Allocates every device
- * buffer the path needs; no later call allocates.
+ * buffer the path needs; no later call allocates.  The row block is given in tiles of the padded M
+ * (ceil(M/32) tile rows in all); a block that reaches into the padding simply holds fewer rows of the caller's A.
  */
 int spamm_plan_create(spamm_plan **out, int M, int K, int N,
                       int row_tile_begin, int row_tile_count, int device);
@@ -111,7 +114,8 @@ int spamm_plan_destroy(spamm_plan *plan);
 
 /*
  * Host->device copies (cuSpAMM.cu:449-450).  a_rows points at the FIRST ROW OF THIS PLAN'S BLOCK
- * (row_tile_begin*32 of the full matrix), leading dimension K; b is the whole of B.  Either may be NULL
+ * (row_tile_begin*32 of the full matrix), leading dimension K (the caller's, unpadded), and holds the rows of the
+ * caller's A that fall into the block; b is the whole of B (K x N, leading dimension N).  Either may be NULL
  * to leave that operand as it is.  Asynchronous on the plan's stream when the host memory is pinned.
  */
 int spamm_upload(spamm_plan *plan, const float *a_rows, const float *b);
@@ -167,12 +171,12 @@ int spamm_peer_wait_selftest(spamm_plan *plan, int senders, unsigned int limit_m
 /* Waits for the plan's stream, then reports a device-side wait that ran out (SPAMM_ERR_DEVICE_WAIT) or SPAMM_OK. */
 int spamm_sync(spamm_plan *plan);
 
-/* Device->host copy of this plan's C rows (leading dimension N) into c_rows; blocking. */
+/* Device->host copy of this plan's rows of C (the caller's N columns, leading dimension N) into c_rows; blocking. */
 int spamm_download_c(spamm_plan *plan, float *c_rows);
 
 /*
- * One call for the whole driver loop body with host matrices in and out (north-star surface:
- * "fp32 host matrices in and out"): upload, norms, lists, pack, multiply, download; blocking.
+ * One call for the whole driver loop body with float host matrices in and out: upload, norms, lists, pack,
+ * multiply, download; blocking.
  * a_rows / c_rows are this plan's row block, b is all of B.  stats may be NULL.
  * Blocks of more than about 64 MiB of A are processed in chunks of rows so that the upload of the next chunk, the
  * kernels of the current one and the download of the previous one overlap (use pinned host memory for that); the
@@ -194,10 +198,12 @@ int spamm_plan_set_chunk_tiles(spamm_plan *plan, int tiles);
  *                          (USINGHALF 1, cuSpAMM.cu:276-392).
  *   SPAMM_PRECISION_SPLIT  float-level accuracy on the tensor cores, in place of the reference's CUDA-core float
  *                          build (USINGHALF 0: cuSpAMM.cu:126-274).  Every operand element x is split as
- *                          hi = half(x), lo = half(x - hi); the product is hi*hi + hi*lo + lo*hi, three tensor-core
- *                          passes over the same lists, float accumulation (lo*lo, about 2^-22 of the result, is
- *                          dropped; elements below 6e-8 in magnitude have no low part).  Norm maps and lists are the
- *                          same in both modes; the multiply takes about three times as long.
+ *                          hi = half(x), lo = half(2^11 * (x - hi)); the product is hi*hi + 2^-11 * (hi*lo + lo*hi),
+ *                          three tensor-core passes over the same lists, float accumulation (lo*lo, about 2^-22 of
+ *                          the result, is dropped).  The scaling keeps the low part out of half's subnormal range,
+ *                          so the mode holds for elements down to about 3e-11 in magnitude (half alone: 6e-8).
+ *                          Norm maps and lists are the same in both modes; the multiply takes about three times as
+ *                          long.
  * Takes effect at the next spamm_pack; allocates a second set of packed-tile buffers the first time.
  */
 enum { SPAMM_PRECISION_HALF = 0, SPAMM_PRECISION_SPLIT = 1 };
@@ -378,6 +384,7 @@ int spamm_count_valid_static_max_blocks(void);
  * Input generators of the reference (host side, float out):
  *   spamm_gen_decay_exp  a_ij = c * v^|i-j|          (getDecayMatrixExp, tool.cu:409-422)
  *   spamm_gen_decay_alg  a_ij = c / (|i-j|^v + 1)    (getDecayMatrixAlg, tool.cu:426-436)
+ *   spamm_gen_ones       a_ij = 1                    (getNormMatrix, tool.cu:370-406: every tile norm is 32)
  * and seeded variants used by the benchmark configurations (sign or magnitude drawn from a counter-based
  * hash of (seed, i, j), so any block of rows can be generated independently):
  *   spamm_gen_signed_exp    a_ij = s_ij * exp(-lambda*|i-j|),  s_ij = +-1
@@ -389,6 +396,7 @@ int spamm_count_valid_static_max_blocks(void);
  */
 int spamm_gen_decay_exp(float *out, float c, float v, int64_t row_begin, int64_t rows, int64_t cols);
 int spamm_gen_decay_alg(float *out, float c, float v, int64_t row_begin, int64_t rows, int64_t cols);
+int spamm_gen_ones(float *out, int64_t row_begin, int64_t rows, int64_t cols);
 int spamm_gen_signed_exp(float *out, double lambda, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols);
 int spamm_gen_uniform_alg(float *out, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols);
 int spamm_gen_uniform(float *out, uint64_t seed, int64_t row_begin, int64_t rows, int64_t cols);

@@ -5,13 +5,13 @@
 # The reference fixes its sizes at compile time (para.h:6-8), so the sources are copied to a scratch directory,
 # the three size constants of para.h are set there, and ref_wrap.cu (launchers only) is compiled next to them.
 # Nothing of the reference is written into this repository; oracle/_ref/ holds build outputs only and is
-# git-ignored.  Needs the reference sources ($SPAMM_REFERENCE_DIR, or the default below) and nvcc; does nothing
-# when they are absent.
+# git-ignored.  Needs the reference sources ($SPAMM_REFERENCE_DIR, or a directory `reference` beside this repository)
+# and nvcc; does nothing when they are absent.
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${SPAMM_REFERENCE_DIR:-/root/reference}"
+REF="${SPAMM_REFERENCE_DIR:-$HERE/../../reference}"
 OUT="$HERE/_ref"
-SIZES="${SPAMM_REF_SIZES:-512 2048}"
+SIZES="${SPAMM_REF_SIZES:-512 2048 8192}"
 if [ ! -f "$REF/cuSpAMM.cu" ]; then echo "reference sources not found at $REF: nothing built"; exit 0; fi
 NVCC="$(command -v nvcc || echo /usr/local/cuda/bin/nvcc)"
 mkdir -p "$OUT"

@@ -38,4 +38,15 @@ int ref_get_c_fp16(const half *d_a, const float *d_norm_a, const half *d_b, cons
     return (int)cudaDeviceSynchronize();
 }
 
+// One pass of the reference's timed region (cuSpAMM.cu:485-531, one device, PART 1) without a synchronisation: the
+// norm map of B, the norm map of A, the gated multiply, on the default stream.  The caller brackets a number of
+// calls with events on that stream to time the reference's kernels on this GPU.
+int ref_timed_step_fp16(const half *d_a, float *d_norm_a, const half *d_b, float *d_norm_b, float *d_c, float norm)
+{
+    unroll_get_Fnorm_FP16<<<K * N / (LoNum * LoNum), 32 * 4>>>(d_b, d_norm_b, K, N, 0);
+    unroll_get_Fnorm_FP16<<<M * K / (LoNum * LoNum), 32 * 4>>>(d_a, d_norm_a, M, K, 0);
+    get_C_FP16_B32<<<(M / LoNum) * (N / LoNum), 32 * 4>>>(d_a, d_norm_a, d_b, d_norm_b, d_c, 0, norm);
+    return (int)cudaGetLastError();
+}
+
 }  // extern "C"

@@ -42,8 +42,9 @@ def test_status_strings(lib):
 def test_argument_validation_needs_no_gpu(lib):
     h = C.c_void_p()
     assert lib.spamm_plan_create(None, 64, 64, 64, 0, 2, 0) == 1
-    assert lib.spamm_plan_create(C.byref(h), 65, 64, 64, 0, 2, 0) == 1        # not a multiple of 32
+    assert lib.spamm_plan_create(C.byref(h), 0, 64, 64, 0, 2, 0) == 1         # empty matrix
     assert lib.spamm_plan_create(C.byref(h), 64, 64, 64, 1, 2, 0) == 1        # row block outside the matrix
+    assert lib.spamm_plan_create(C.byref(h), 65, 64, 64, 1, 3, 0) == 1        # 65 rows are 3 tile rows, not 4
     assert lib.spamm_plan_create(C.byref(h), 64, 32 * 70000, 64, 0, 2, 0) == 6  # k index does not fit 16 bits
     assert lib.spamm_plan_destroy(None) == 0
     assert lib.spamm_norms(None) == 1

@@ -184,3 +184,48 @@ def test_cnn_im2col_shape_with_padding(oracle):
     dense = W[:60, :570].astype(np.float16).astype(np.float64) @ X[:570, :4000].astype(np.float16).astype(np.float64)
     assert rel_fro(Cp[:60, :4000], dense) < 1e-5
     assert not Cp[60:].any()
+
+
+def test_cnn_im2col_full_shape(oracle):
+    """The reference's CNN case at its full size (para.h:19-22): 64 x 576 weights times a 576 x 102400 im2col matrix
+    (synthetic stand-ins for the missing data files, same shapes)."""
+    from cuspamm_b200 import SpammPlan
+
+    rng = np.random.default_rng(10)
+    W = (rng.standard_normal((64, 576)) * np.exp(-4 * rng.random((64, 576)))).astype(np.float32)
+    X = (rng.standard_normal((576, 102400), dtype=np.float32) *
+         np.exp(-4 * rng.random((576, 102400), dtype=np.float32))).astype(np.float32)
+    tau = 127.0
+    C_ref, S, nA, nB, counts = oracle.spamm(W, X, tau, want_maps=True)
+    with SpammPlan(64, 576, 102400) as p:
+        C, st = p.multiply(W, X, tau)
+        assert np.array_equal(p.norm_b().view(np.uint32), nB.view(np.uint32))
+        got_counts, _ = p.counts()
+    assert st["survivors"] == S and 0 < S < st["tile_products"]
+    assert np.array_equal(got_counts, counts)
+    assert rel_fro(C, C_ref) <= C_TOL
+
+
+def test_command_line_driver(oracle):
+    """cuspamm_b200/spamm_main, the C++ caller of the boundary with the shape of the reference's `main`: its default
+    run (2048^3, c/(|i-j|^v+1) with c=v=0.1, Norm=1.548969; para.h:2,6-8,14) keeps as many products as the checker, and
+    the all-ones input keeps all of them at the threshold 1024."""
+    import re
+    import subprocess
+
+    from cuspamm_b200 import build, gen_decay_alg
+
+    exe = build.build_driver()
+    A = gen_decay_alg(0.1, 0.1, 2048, 2048)
+    _, S = oracle.spamm(A, A.copy(), 1.548969)
+    r = subprocess.run([str(exe), "--iters", "3", "--warmup", "1"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                       text=True, timeout=300)
+    assert r.returncode == 0, r.stdout
+    assert int(re.search(r"valid mul=(\d+)", r.stdout).group(1)) == S
+    assert re.search(r"SpAMM time=\d", r.stdout)
+    r = subprocess.run([str(exe), "--n", "250", "--matrix", "ones", "--tau", "1000", "--iters", "2", "--warmup", "1"],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout
+    # 250 = 7 full tiles + a 26-wide rest: the products of full tiles (32*32 = 1024) pass 1000, those with a
+    # partial tile (32*sqrt(32*26) = 923, or 26*32 = 832) do not
+    assert int(re.search(r"valid mul=(\d+)", r.stdout).group(1)) == 7 ** 3

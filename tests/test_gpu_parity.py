@@ -361,3 +361,144 @@ def test_split_precision_reaches_float_accuracy(oracle):
         p.set_chunk_tiles(64)
         C, st = p.multiply(A, B, tau)
         assert st["survivors"] == S and rel_fro(C, C_exact) <= 1e-5
+
+
+def test_all_ones_known_answer():
+    """The reference's all-ones input (getNormMatrix, tool.cu:370-406): every tile norm is exactly 32, every norm
+    product exactly 1024, so the threshold 1024 keeps every product (the comparison is >=) and the next float above it
+    keeps none; with all kept, every element of C is K."""
+    from cuspamm_b200 import SpammPlan, gen_ones
+
+    n = 256
+    A, B = gen_ones(n, n), gen_ones(n, n)
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        p.run(1024.0)
+        p.sync()
+        assert np.array_equal(p.norm_a(), np.full((8, 8), 32.0, dtype=np.float32))
+        assert np.array_equal(p.norm_b(), np.full((8, 8), 32.0, dtype=np.float32))
+        counts, S = p.counts()
+        assert S == 8 ** 3 and np.array_equal(counts, np.full((8, 8), 8, dtype=np.int32))
+        assert np.array_equal(p.download_c(), np.full((n, n), float(n), dtype=np.float32))
+        p.run(float(np.nextafter(np.float32(1024.0), np.float32(2048.0))))
+        p.sync()
+        assert p.counts()[1] == 0 and not p.download_c().any()
+
+
+def test_identity_known_answer(oracle):
+    """A = I: tile norms sqrt(32) on the diagonal and 0 elsewhere, so the list of C(i,j) is {i} exactly where
+    sqrt(32) * ||B(i,j)|| >= tau, and C equals the half-rounded B on those tiles and zero on the others."""
+    from cuspamm_b200 import SpammPlan
+
+    n = 256
+    A = np.eye(n, dtype=np.float32)
+    B = signed_decay(n, 0.2, seed=5)
+    nB = oracle.norm_map(B)
+    keep = (np.float32(np.sqrt(np.float32(32.0))) * nB) >= np.float32(0.5)
+    assert keep.any() and not keep.all()
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        p.run(0.5)
+        p.sync()
+        counts, S = p.counts()
+        offsets, kidx = p.lists()
+        C = p.download_c()
+    assert np.array_equal(counts, keep.astype(np.int32)) and S == int(keep.sum())
+    rows = np.repeat(np.arange(8), 8).reshape(8, 8)
+    assert np.array_equal(kidx, rows[keep])
+    want = oracle.round_to_half(B).reshape(8, 32, 8, 32) * keep[:, None, :, None]
+    assert np.array_equal(C, want.reshape(n, n))
+
+
+@pytest.mark.parametrize("precision", ["half", "split"])
+def test_repeated_multiply_on_the_same_lists(oracle, precision):
+    """spamm_gated_multiply may be called again on the same lists: every call must rebuild all of C, whichever of the
+    two multiply kernels owns a macro tile.  A matrix whose upper rows are dense (those macro tiles go to pairs of
+    SMs) and whose lower rows are gated; C is overwritten with garbage between the calls."""
+    import torch
+
+    from cuspamm_b200 import BUF_C, SpammPlan
+
+    M, K, N = 768, 256, 768
+    rng = np.random.default_rng(31)
+    A = rng.uniform(0.5, 1.0, (M, K)).astype(np.float32)
+    B = rng.uniform(0.5, 1.0, (K, N)).astype(np.float32)
+    # lower third: every tile scaled by its own factor around 1, so that some of its products pass and some do not
+    A[512:] *= np.repeat(np.repeat(rng.uniform(0.5, 1.2, (8, K // 32)), 32, axis=0), 32, axis=1).astype(np.float32)
+    nA, nB = oracle.norm_map(A), oracle.norm_map(B)
+    tau = float(np.min(nA[:16, :, None] * nB[None])) * 0.999              # every product of the upper rows survives
+    C_ref, S = (oracle.spamm_exact if precision == "split" else oracle.spamm)(A, B, tau)
+    counts, _, _ = oracle.lists(nA, nB, tau)
+    low = counts[16:]
+    assert (counts[:16] == K // 32).all() and (low < K // 32).any() and (low > 0).any() and S > 0
+    with SpammPlan(M, K, N) as p:
+        p.set_precision(precision)
+        p.upload(A, B)
+        p.run(tau)
+        p.sync()                       # the hints now say "mostly dense": the next multiply launches the two-SM kernel
+        p.run(tau)
+        p.sync()
+        first = p.download_c()
+        assert rel_fro(first, C_ref) <= (1e-5 if precision == "split" else C_TOL)
+        for _ in range(3):
+            p.as_tensor(BUF_C).fill_(float("nan"))
+            torch.cuda.synchronize()
+            p.gated_multiply()
+            p.sync()
+            assert np.array_equal(p.download_c(), first)
+
+
+def test_sizes_that_are_not_multiples_of_32(oracle):
+    """The library pads on the GPU (main.h:54-56): host matrices keep their own sizes and leading dimensions on the way
+    in and out, the result equals the checker's on zero-padded copies, also per row block and through the pipelined
+    host-to-host call."""
+    from cuspamm_b200 import SpammPlan, pad_to_tiles
+
+    rng = np.random.default_rng(41)
+    M, K, N = 203, 570, 333
+    A = (rng.standard_normal((M, K)) * np.exp(-rng.random((M, K)) * 5)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * np.exp(-rng.random((K, N)) * 5)).astype(np.float32)
+    Ap, Bp = pad_to_tiles(A), pad_to_tiles(B)
+    tau = float(np.median(oracle.norm_map(Ap)[:, :, None] * oracle.norm_map(Bp)[None]))
+    C_ref, S, nA, nB, counts = oracle.spamm(Ap, Bp, tau, want_maps=True)
+    with SpammPlan(M, K, N) as p:
+        assert (p.row_tile_count, p.k_tiles, p.n_tiles, p.rows) == (7, 18, 11, M)
+        p.upload(A, B)
+        p.run(tau)
+        p.sync()
+        assert np.array_equal(p.norm_a().view(np.uint32), nA.view(np.uint32))
+        assert np.array_equal(p.norm_b().view(np.uint32), nB.view(np.uint32))
+        got_counts, got_s = p.counts()
+        assert got_s == S and np.array_equal(got_counts, counts)
+        C = p.download_c()
+        assert C.shape == (M, N) and rel_fro(C, C_ref[:M, :N]) <= C_TOL
+        for chunk in (4, 64):
+            p.set_chunk_tiles(chunk)
+            C2, st = p.multiply(A, B, tau)
+            assert st["survivors"] == S and rel_fro(C2, C_ref[:M, :N]) <= C_TOL
+    # the last row block ends inside the padding: it holds 203 - 4*32 = 75 rows of the caller's matrices
+    with SpammPlan(M, K, N, 4, 3) as q:
+        assert q.rows == 75
+        q.upload(np.ascontiguousarray(A[128:]), B)
+        q.run(tau)
+        q.sync()
+        assert q.counts()[1] == int(counts[4:].sum())
+        assert rel_fro(q.download_c(), C_ref[128:M, :N]) <= C_TOL
+
+
+def test_split_precision_on_small_magnitudes(oracle):
+    """Inputs four orders of magnitude below 1: the low parts are stored scaled by 2^11, so they stay normal halves and
+    the float-accuracy mode keeps its accuracy where unscaled residuals would fall into half's subnormal range."""
+    from cuspamm_b200 import SpammPlan
+
+    n = 256
+    A = signed_decay(n, 0.02, seed=93) * np.float32(1e-4)
+    B = signed_decay(n, 0.03, seed=94) * np.float32(1e-4)
+    C_exact, S = oracle.spamm_exact(A, B, 0.0)
+    with SpammPlan(n, n, n) as p:
+        p.upload(A, B)
+        p.set_precision("split")
+        p.run(0.0)
+        p.sync()
+        assert p.counts()[1] == S
+        assert rel_fro(p.download_c(), C_exact) <= 1e-5
