@@ -55,6 +55,20 @@ SIGNATURES = {
     "spamm_peer_handles": (_i, [_vp, _vp, _sz]),
     "spamm_peer_attach": (_i, [_vp, _i, _i, _vp]),
     "spamm_norm_b_share_push": (_i, [_vp, _i, _i]),
+    "spamm_run_shared": (_i, [_vp, _f, _i, _i]),
+    "spamm_norms_shared": (_i, [_vp, _i, _i]),
+    "spamm_upload_b_rows": (_i, [_vp, _vp, _i, _i]),
+    "spamm_multiply_b_resident": (_i, [_vp, _vp, _vp, _f, _vp, C.POINTER(SpammStats)]),
+    "spamm_group_create": (_i, [_pp, _i, _i, _i, _i, C.POINTER(_i)]),
+    "spamm_group_destroy": (_i, [_vp]),
+    "spamm_group_size": (_i, [_vp]),
+    "spamm_group_plan": (_i, [_vp, _i, _pp]),
+    "spamm_group_upload": (_i, [_vp, _vp, _vp]),
+    "spamm_group_run": (_i, [_vp, _f]),
+    "spamm_group_sync": (_i, [_vp]),
+    "spamm_group_download_c": (_i, [_vp, _vp]),
+    "spamm_group_survivors": (_i, [_vp, C.POINTER(_i64)]),
+    "spamm_group_multiply": (_i, [_vp, _vp, _vp, _vp, _f, C.POINTER(SpammStats)]),
     "spamm_peer_wait_selftest": (_i, [_vp, _i, C.c_uint]),
     "spamm_build_lists": (_i, [_vp, _f]),
     "spamm_pack": (_i, [_vp]),

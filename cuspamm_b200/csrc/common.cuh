@@ -48,8 +48,10 @@ struct PeerWait {                     // what the list builder waits for before 
 };
 constexpr unsigned long long PEER_WAIT_LIMIT_NS = 2000000000ull;
 int peer_wait_selftest_launch(const PeerWait &w, cudaStream_t stream);
-int norm_map_push_launch(const float *d_x, int rows, int cols, int64_t ld, int64_t map_offset, const PeerTargets &t,
-                         int rank, unsigned int epoch, cudaStream_t stream);
+// Stores `share` floats of this GPU's map of B (at d_local_share = t.map[rank] + map_offset) into every other GPU's map
+// and raises this GPU's arrival flag, value `epoch`, on every GPU.
+int push_share_launch(const float *d_local_share, int64_t share, int64_t map_offset, const PeerTargets &t, int rank,
+                      unsigned int epoch, cudaStream_t stream);
 // Both norm maps AND the half conversion of every tile of A and B in one launch (for mostly surviving workloads).
 int norm_pack_pair_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a, void *d_half_a,
                           const float *d_xb, int rows_b, int cols_b, int64_t ldb, float *d_map_b, void *d_half_b,

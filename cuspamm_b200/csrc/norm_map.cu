@@ -231,20 +231,15 @@ push_share_kernel(const float4 *__restrict__ src, int64_t vecs, int64_t map_offs
     }
 }
 
-int norm_map_push_launch(const float *d_x, int rows, int cols, int64_t ld, int64_t map_offset, const PeerTargets &t,
-                         int rank, unsigned int epoch, cudaStream_t stream)
+int push_share_launch(const float *d_local_share, int64_t share, int64_t map_offset, const PeerTargets &t, int rank,
+                      unsigned int epoch, cudaStream_t stream)
 {
-    if (!d_x || rows <= 0 || cols <= 0 || rows % TILE || cols % TILE || (ld & 3) || t.n <= 0 || t.n > MAX_PEERS ||
-        rank < 0 || rank >= t.n)
-        return SPAMM_ERR_INVALID;
-    const int tile_rows = rows / TILE, tile_cols = cols / TILE;
-    const int64_t share = (int64_t)tile_rows * tile_cols;          // floats in this GPU's share of the map
-    float *local = t.map[rank] + map_offset;
-    if ((share & 3) || (map_offset & 3) || (reinterpret_cast<uintptr_t>(local) & 15)) return SPAMM_ERR_UNSUPPORTED;
-    int st = spamm_norm_map_dev(d_x, rows, cols, ld, local, stream);
-    if (st) return st;
-    push_share_kernel<<<t.n, 256, 0, stream>>>(reinterpret_cast<const float4 *>(local), share / 4, map_offset / 4, t,
-                                              rank, epoch);
+    if (!d_local_share || share <= 0 || t.n <= 0 || t.n > MAX_PEERS || rank < 0 || rank >= t.n) return SPAMM_ERR_INVALID;
+    if ((share & 3) || (map_offset & 3) || (reinterpret_cast<uintptr_t>(d_local_share) & 15) ||
+        d_local_share != t.map[rank] + map_offset)
+        return SPAMM_ERR_UNSUPPORTED;
+    push_share_kernel<<<t.n, 256, 0, stream>>>(reinterpret_cast<const float4 *>(d_local_share), share / 4,
+                                              map_offset / 4, t, rank, epoch);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -8,7 +8,7 @@
 #include <string>
 #include <vector>
 
-#include "common.cuh"
+#include "plan.cuh"
 
 namespace spamm {
 
@@ -24,114 +24,38 @@ int record_cuda_error(cudaError_t e, const char *what)
 // Stores a detail message for spamm_last_cuda_error when the failing call is not a CUDA runtime call.
 void record_error_text(const char *text) { g_last_cuda_error = text; }
 
-// The kernels' counters live at the head of the buffer that is cleared before every list build: one set for the
-// whole block of rows, or one per chunk of rows when spamm_multiply pipelines the copies with the kernels.
-using DeviceScalars = spamm_list_scalars;
-constexpr int MAX_CHUNKS = 64;
-constexpr size_t CHUNK_TARGET_BYTES = size_t(64) << 20;    // rows of A copied per pipeline step
+int copy_matrix(float *dst, size_t dst_ld, const float *src, size_t src_ld, size_t rows, size_t cols,
+                cudaMemcpyKind kind, cudaStream_t stream)
+{
+    if (rows == 0 || cols == 0) return SPAMM_OK;
+    if (dst_ld == cols && src_ld == cols)
+        SPAMM_CUDA_TRY(cudaMemcpyAsync(dst, src, sizeof(float) * rows * cols, kind, stream));
+    else
+        SPAMM_CUDA_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * dst_ld, src, sizeof(float) * src_ld, sizeof(float) * cols,
+                                         rows, kind, stream));
+    return SPAMM_OK;
+}
+
+int plan_attach_direct(spamm_plan *p, int world, int rank, spamm_plan *const *all)
+{
+    if (!p || !all || world < 2 || world > MAX_PEERS || rank < 0 || rank >= world) return SPAMM_ERR_INVALID;
+    if (p->peer_world) return SPAMM_ERR_STATE;
+    for (int r = 0; r < world; r++) {
+        if (!all[r] || all[r]->k_tiles != p->k_tiles || all[r]->n_tiles != p->n_tiles) return SPAMM_ERR_INVALID;
+        p->peer_norm_b[r][0] = all[r]->d_norm_b_buf[0];
+        p->peer_norm_b[r][1] = all[r]->d_norm_b_buf[1];
+        p->peer_flags[r] = all[r]->d_peer_flags;
+    }
+    p->peer_world = world;
+    p->peer_rank = rank;
+    return SPAMM_OK;
+}
 
 }  // namespace spamm
 
 using namespace spamm;
 
-struct spamm_plan {
-    int M = 0, K = 0, N = 0;            // padded to multiples of 32 (main.h:54-56): the sizes every kernel works on
-    int in_M = 0, in_K = 0, in_N = 0;   // the caller's sizes: leading dimensions and extents of the host matrices
-    int row_begin = 0, row_tiles = 0;   // in tiles
-    int k_tiles = 0, n_tiles = 0, mi_n = 0, mj_n = 0;
-    int device = 0;
-    cudaStream_t stream = nullptr;
-    float *d_a = nullptr, *d_b = nullptr, *d_c = nullptr;
-    float *d_norm_a = nullptr, *d_norm_b = nullptr;
-    int32_t *d_counts = nullptr, *d_step_counts = nullptr;
-    uint32_t *d_steps = nullptr;
-    uint8_t *d_half_a = nullptr, *d_half_b = nullptr;
-    uint8_t *d_low_a = nullptr, *d_low_b = nullptr;     // split precision: packed half(x - half(x)), allocated on demand
-    int precision = SPAMM_PRECISION_HALF;
-    int32_t *d_order = nullptr;         // macro-tile visiting order of the multiply kernel
-    int32_t *d_busy = nullptr;          // macro tiles that have steps
-    uint32_t *d_tile_list = nullptr;    // tiles to convert to half
-    void *d_list_scratch = nullptr;     // chunk maxima of the list builder
-    uint8_t *d_cleared = nullptr;       // [DeviceScalars | need_a | need_b], cleared per list build
-    size_t cleared_bytes = 0, need_a_off = 0, need_b_off = 0;
-    DeviceScalars *h_scalars = nullptr; // pinned
-    void *d_cv_scratch = nullptr;       // partial sums of the valid-product counter
-    size_t cv_scratch_bytes = 0;
-    void *d_err_scratch = nullptr;      // block partials + 3 doubles of spamm_error_norms
-    unsigned long long *d_cv_count = nullptr;   // [count, sum(double)] on the device
-    unsigned long long *h_cv = nullptr;         // pinned mirror of the two
-    cudaEvent_t ev[8] = {};
-    cudaStream_t stream_d2h = nullptr;  // second stream: copies C chunks out while the next chunk is computed
-    cudaEvent_t ev_chunk[MAX_CHUNKS] = {};
-    cudaStream_t stream_h2d = nullptr;  // third stream: uploads of the pipelined spamm_multiply, back to back
-    cudaEvent_t ev_up[MAX_CHUNKS + 2] = {};      // [c]: rows of chunk c are on the GPU; [MAX_CHUNKS]: B is; [+1]: entry fence
-    cudaEvent_t ev_zero[2] = {};        // fork / join of the early clearing of C on the second stream
-    int zero_hint = -1;                 // last counters read: did at most a quarter of the macro tiles have steps
-    bool c_zero_pending = false;        // C is being cleared on the second stream; the multiply writes busy tiles only
-    int chunk_tiles = 0;                // tile rows per chunk of the pipelined spamm_multiply (multiple of 4)
-    int n_chunks = 1;
-    int32_t *d_order_chunk = nullptr, *d_order_last = nullptr;   // macro-tile orders for a full / the last chunk
-
-    int active_scalars = 1;             // how many sets of counters the last operation used (one per chunk)
-    bool queues_clean = false;          // the multiply's two work counters are zero (cleared by the list build or the packing kernel)
-    int dense_hint = -1;                // last counters read: were at least half of the macro tiles dense (-1: unknown)
-    int pack_mode = SPAMM_PACK_AUTO;    // which tiles are converted to half, see spamm_plan_set_pack_mode
-    int pack_all_hint = -1;             // last counters read: did the lists name at least half of all tiles (-1: unknown)
-    bool packed_all = false;            // the last spamm_norms converted every tile: spamm_pack has nothing to do
-    // peer exchange of B's norm-map shares (one process per GPU, see spamm_peer_attach)
-    float *d_norm_b_buf[2] = {nullptr, nullptr};   // B's map, double buffered by step parity; d_norm_b is the current
-    unsigned int *d_peer_flags = nullptr;          // [MAX_PEERS] arrival flags + [1] block counter of the push kernel
-    int *d_peer_error = nullptr;
-    int *h_peer_error = nullptr;                   // pinned
-    int peer_world = 0, peer_rank = 0;
-    unsigned int peer_epoch = 0;
-    bool peer_wait_pending = false;
-    void *peer_mapped[MAX_PEERS][3] = {};          // what cudaIpcOpenMemHandle returned, per peer
-    float *peer_norm_b[MAX_PEERS][2] = {};
-    unsigned int *peer_flags[MAX_PEERS] = {};      // every peer's arrival flags, as mapped into this process
-    bool have_norms = false, have_lists = false, have_pack = false;
-    int64_t launches = 0;
-
-    DeviceScalars *scalars() const { return reinterpret_cast<DeviceScalars *>(d_cleared); }
-    // rows of the caller's A (and C) that fall into this plan's block: the last block may end inside the padding
-    int rows_in() const
-    {
-        const int64_t left = (int64_t)in_M - (int64_t)row_begin * TILE;
-        const int64_t mine = (int64_t)row_tiles * TILE;
-        return (int)(left < 0 ? 0 : (left < mine ? left : mine));
-    }
-    bool padded() const { return in_M != M || in_K != K || in_N != N; }
-    uint8_t *need_a() const { return d_cleared + need_a_off; }
-    uint8_t *need_b() const { return d_cleared + need_b_off; }
-    size_t bytes_a() const { return sizeof(float) * (size_t)row_tiles * TILE * K; }
-    size_t bytes_b() const { return sizeof(float) * (size_t)K * N; }
-    size_t bytes_c() const { return sizeof(float) * (size_t)row_tiles * TILE * N; }
-    size_t bytes_norm_a() const { return sizeof(float) * (size_t)row_tiles * k_tiles; }
-    size_t bytes_norm_b() const { return sizeof(float) * (size_t)k_tiles * n_tiles; }
-    size_t bytes_counts() const { return sizeof(int32_t) * (size_t)row_tiles * n_tiles; }
-    size_t n_mt() const { return (size_t)mi_n * mj_n; }
-    size_t step_cap() const { return (size_t)STEP_CAP_PER_K * k_tiles; }
-    size_t bytes_steps() const { return sizeof(uint32_t) * n_mt() * step_cap(); }
-    size_t bytes_step_counts() const { return sizeof(int32_t) * n_mt(); }
-    size_t bytes_half_a() const { return (size_t)mi_n * k_tiles * A_SLAB_BYTES; }
-    size_t bytes_half_b() const { return (size_t)k_tiles * mj_n * B_SLAB_BYTES; }
-};
-
 namespace {
-
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = true;
-    explicit DeviceGuard(int dev)
-    {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
-    }
-    ~DeviceGuard()
-    {
-        if (prev >= 0) cudaSetDevice(prev);
-    }
-};
 
 template <typename T>
 int dev_alloc(T **p, size_t bytes)
@@ -147,20 +71,6 @@ int dev_alloc(T **p, size_t bytes)
 }
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-// rows x cols floats between a host matrix (leading dimension h_ld) and a device matrix (leading dimension d_ld);
-// one flat copy when both are packed the same way
-int copy_matrix(float *dst, size_t dst_ld, const float *src, size_t src_ld, size_t rows, size_t cols,
-                cudaMemcpyKind kind, cudaStream_t stream)
-{
-    if (rows == 0 || cols == 0) return SPAMM_OK;
-    if (dst_ld == cols && src_ld == cols)
-        SPAMM_CUDA_TRY(cudaMemcpyAsync(dst, src, sizeof(float) * rows * cols, kind, stream));
-    else
-        SPAMM_CUDA_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * dst_ld, src, sizeof(float) * src_ld, sizeof(float) * cols,
-                                         rows, kind, stream));
-    return SPAMM_OK;
-}
 
 // Zeroes the counters and need flags the list builder starts from, except the error and overflow words of every set
 // of counters: those stay until read_scalars has shown them to the host.
@@ -352,9 +262,13 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
         if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess)
             return fail(record_cuda_error(cudaGetLastError(), "cudaEventCreate"));
     {
-        // chunking of the pipelined path: about 64 MiB of A rows per chunk, whole macro-tile rows, at most 64 chunks
+        // chunking of the pipelined path: an eighth of the block's rows of A per chunk, between 16 and 64 MiB (a block
+        // of at most 16 MiB goes in one piece), whole macro-tile rows, at most 64 chunks
         const size_t row_bytes = sizeof(float) * (size_t)TILE * K;
-        int ct = (int)((CHUNK_TARGET_BYTES + row_bytes - 1) / row_bytes);
+        size_t target = p->bytes_a() / 8;
+        if (target < CHUNK_MIN_BYTES) target = CHUNK_MIN_BYTES;
+        if (target > CHUNK_TARGET_BYTES) target = CHUNK_TARGET_BYTES;
+        int ct = (int)((target + row_bytes - 1) / row_bytes);
         ct = (ct + MT_R - 1) / MT_R * MT_R;
         while (p->row_tiles > 0 && ceil_div(p->row_tiles, ct) > MAX_CHUNKS) ct += MT_R;
         p->chunk_tiles = ct;
@@ -534,7 +448,17 @@ int spamm_peer_attach(spamm_plan *p, int world, int rank, const void *all_handle
         }
         for (int i = 0; i < 3; i++) {
             cudaError_t e = cudaIpcOpenMemHandle(&p->peer_mapped[r][i], h[r * 3 + i], cudaIpcMemLazyEnablePeerAccess);
-            if (e != cudaSuccess) return record_cuda_error(e, "cudaIpcOpenMemHandle");
+            if (e != cudaSuccess) {
+                // leave nothing half attached: close what was opened so far, so that a retry starts clean
+                p->peer_mapped[r][i] = nullptr;
+                for (int rr = 0; rr <= r; rr++)
+                    for (int ii = 0; ii < 3; ii++)
+                        if (p->peer_mapped[rr][ii]) {
+                            cudaIpcCloseMemHandle(p->peer_mapped[rr][ii]);
+                            p->peer_mapped[rr][ii] = nullptr;
+                        }
+                return record_cuda_error(e, "cudaIpcOpenMemHandle");
+            }
         }
         p->peer_norm_b[r][0] = static_cast<float *>(p->peer_mapped[r][0]);
         p->peer_norm_b[r][1] = static_cast<float *>(p->peer_mapped[r][1]);
@@ -561,7 +485,9 @@ int spamm_peer_wait_selftest(spamm_plan *p, int senders, unsigned int limit_ms)
     return expired ? SPAMM_ERR_DEVICE_WAIT : SPAMM_OK;
 }
 
-int spamm_norm_b_share_push(spamm_plan *p, int b_tile_begin, int b_tile_count)
+// Norm map of this GPU's share of B (and, with `with_a`, of its rows of A in the same launch), then the small kernel
+// that stores the share into every other GPU's map and raises the arrival flags.
+static int norm_share_and_push(spamm_plan *p, int b_tile_begin, int b_tile_count, bool with_a)
 {
     if (!p || b_tile_begin < 0 || b_tile_count <= 0 || b_tile_begin + (int64_t)b_tile_count > p->k_tiles)
         return SPAMM_ERR_INVALID;
@@ -578,14 +504,41 @@ int spamm_norm_b_share_push(spamm_plan *p, int b_tile_begin, int b_tile_count)
         t.map[r] = p->peer_norm_b[r][buf];
         t.flags[r] = p->peer_flags[r];
     }
-    int st = norm_map_push_launch(p->d_b + (size_t)b_tile_begin * TILE * p->N, b_tile_count * TILE, p->N, p->N,
-                                  (int64_t)b_tile_begin * p->n_tiles, t, p->peer_rank, p->peer_epoch, p->stream);
+    const float *b_share = p->d_b + (size_t)b_tile_begin * TILE * p->N;
+    const int64_t map_offset = (int64_t)b_tile_begin * p->n_tiles;
+    int st;
+    if (with_a && p->row_tiles)
+        st = spamm_norm_map_pair_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, b_share, b_tile_count * TILE,
+                                     p->N, p->N, p->d_norm_b + map_offset, p->stream);
+    else
+        st = spamm_norm_map_dev(b_share, b_tile_count * TILE, p->N, p->N, p->d_norm_b + map_offset, p->stream);
     if (st) return st;
+    if ((st = push_share_launch(p->d_norm_b + map_offset, (int64_t)b_tile_count * p->n_tiles, map_offset, t, p->peer_rank,
+                                p->peer_epoch, p->stream)))
+        return st;
     p->launches += 2;
     p->peer_wait_pending = true;
     p->have_lists = p->have_pack = false;
     p->packed_all = false;
+    if (with_a) p->have_norms = true;
     return SPAMM_OK;
+}
+
+int spamm_norm_b_share_push(spamm_plan *p, int b_tile_begin, int b_tile_count)
+{
+    return norm_share_and_push(p, b_tile_begin, b_tile_count, false);
+}
+
+int spamm_norms_shared(spamm_plan *p, int b_tile_begin, int b_tile_count)
+{
+    return norm_share_and_push(p, b_tile_begin, b_tile_count, true);
+}
+
+int spamm_run_shared(spamm_plan *p, float tau, int b_tile_begin, int b_tile_count)
+{
+    int st = norm_share_and_push(p, b_tile_begin, b_tile_count, true);
+    if (st) return st;
+    return spamm_finish(p, tau);
 }
 
 int spamm_norms(spamm_plan *p)
@@ -867,30 +820,58 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
     return SPAMM_OK;
 }
 
+int spamm_upload_b_rows(spamm_plan *p, const float *b_rows, int row_begin, int rows)
+{
+    if (!p || !b_rows || row_begin < 0 || rows < 0 || row_begin + (int64_t)rows > p->in_K) return SPAMM_ERR_INVALID;
+    DeviceGuard guard(p->device);
+    int st = copy_matrix(p->d_b + (size_t)row_begin * p->N, p->N, b_rows, p->in_N, rows, p->in_N, cudaMemcpyHostToDevice,
+                         p->stream);
+    if (st) return st;
+    p->have_norms = p->have_lists = p->have_pack = false;
+    return SPAMM_OK;
+}
+
+static int multiply_impl(spamm_plan *p, const float *a_rows, const float *b, float *c_rows, float tau,
+                         cudaEvent_t b_ready, spamm_stats *stats)
+{
+    int st = plan_multiply_issue(p, a_rows, b, c_rows, tau, b_ready);
+    if (st) return st;
+    return plan_multiply_finish(p, stats);
+}
+
 int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_rows, float tau, spamm_stats *stats)
 {
     if (!p || !a_rows || !b || !c_rows) return SPAMM_ERR_INVALID;
+    return multiply_impl(p, a_rows, b, c_rows, tau, nullptr, stats);
+}
+
+int spamm_multiply_b_resident(spamm_plan *p, const float *a_rows, float *c_rows, float tau, void *b_ready_event,
+                              spamm_stats *stats)
+{
+    if (!p || !a_rows || !c_rows) return SPAMM_ERR_INVALID;
+    return multiply_impl(p, a_rows, nullptr, c_rows, tau, static_cast<cudaEvent_t>(b_ready_event), stats);
+}
+
+}  // extern "C"
+
+// The asynchronous part of spamm_multiply: everything is queued, nothing is waited for.
+// b == nullptr: B is in the plan's buffer already, or will be once `b_ready` (may be null) has completed.
+int spamm::plan_multiply_issue(spamm_plan *p, const float *a_rows, const float *b, float *c_rows, float tau,
+                               cudaEvent_t b_ready)
+{
     DeviceGuard guard(p->device);
     int st;
-    if (p->n_chunks <= 1 || p->row_tiles == 0) {
+    p->multiply_chunked = !(p->n_chunks <= 1 || p->row_tiles == 0);
+    if (!p->multiply_chunked) {
         // small problem: one pass, phase by phase
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev[5], p->stream));
+        if (b_ready) SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, b_ready, 0));
         if ((st = spamm_upload(p, a_rows, b))) return st;
         if ((st = run_with_events(p, tau))) return st;
         if ((st = copy_matrix(c_rows, p->in_N, p->d_c, p->N, p->rows_in(), p->in_N, cudaMemcpyDeviceToHost, p->stream)))
             return st;
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev[6], p->stream));
-        if ((st = read_scalars(p))) return st;
-        if (stats) {
-            memset(stats, 0, sizeof(*stats));
-            if ((st = phase_times(p, stats))) return st;
-            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
-            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_d2h, p->ev[4], p->ev[6]));
-            fill_stats(p, stats);
-            stats->steps = sum_step_counts(p, &st);
-            if (st) return st;
-        }
-        return status_from_scalars(p);
+        return SPAMM_OK;
     }
 
     // Large problem: the copies dominate (PCIe), so they are overlapped with each other and with the kernels.
@@ -908,7 +889,8 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
     // stream, which may still read the old matrices); the main stream waits for B, then for each chunk of rows.
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[MAX_CHUNKS + 1], p->stream));
     SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream_h2d, p->ev_up[MAX_CHUNKS + 1], 0));
-    if ((st = copy_matrix(p->d_b, p->N, b, p->in_N, p->in_K, p->in_N, cudaMemcpyHostToDevice, p->stream_h2d))) return st;
+    if (b && (st = copy_matrix(p->d_b, p->N, b, p->in_N, p->in_K, p->in_N, cudaMemcpyHostToDevice, p->stream_h2d)))
+        return st;
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[MAX_CHUNKS], p->stream_h2d));
     const int rows_in = p->rows_in();
     // rows of the caller's matrices inside a chunk of tile rows (the last chunk may reach into the padding)
@@ -925,6 +907,7 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
         SPAMM_CUDA_TRY(cudaEventRecord(p->ev_up[c], p->stream_h2d));
     }
     SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_up[MAX_CHUNKS], 0));
+    if (b_ready) SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, b_ready, 0));   // somebody else is still writing B
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[0], p->stream));
     if ((st = spamm_norm_map_dev(p->d_b, p->K, p->N, p->N, p->d_norm_b, p->stream))) return st;
     p->launches++;
@@ -949,18 +932,34 @@ int spamm_multiply(spamm_plan *p, const float *a_rows, const float *b, float *c_
     SPAMM_CUDA_TRY(cudaEventRecord(p->ev[6], p->stream));
     p->have_norms = p->have_lists = true;
     p->have_pack = false;       // the per-chunk work lists are not those of a whole-block multiply
+    return SPAMM_OK;
+}
+
+// The blocking part: waits for what plan_multiply_issue queued, reads the counters, fills the statistics.
+int spamm::plan_multiply_finish(spamm_plan *p, spamm_stats *stats)
+{
+    DeviceGuard guard(p->device);
+    int st;
     if ((st = read_scalars(p))) return st;
     if (stats) {
         memset(stats, 0, sizeof(*stats));
-        // the phases interleave with the copies here: only the whole call is timed (spamm_run_timed gives phases)
-        SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_device_total, p->ev[5], p->ev[6]));
-        SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
+        if (!p->multiply_chunked) {
+            if ((st = phase_times(p, stats))) return st;
+            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
+            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_d2h, p->ev[4], p->ev[6]));
+        } else {
+            // the phases interleave with the copies: only the whole call is timed (spamm_run_timed gives phases)
+            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_device_total, p->ev[5], p->ev[6]));
+            SPAMM_CUDA_TRY(cudaEventElapsedTime(&stats->ms_h2d, p->ev[5], p->ev[0]));
+        }
         fill_stats(p, stats);
         stats->steps = sum_step_counts(p, &st);
         if (st) return st;
     }
     return status_from_scalars(p);
 }
+
+extern "C" {
 
 int spamm_get_norm_a(spamm_plan *p, float *out)
 {

@@ -147,13 +147,29 @@ class SpammPlan:
         self.row_tile_begin, self.row_tile_count = row_tile_begin, row_tile_count
         self.device = device
         self._h = C.c_void_p()
+        self._owned = True
         check(self._lib.spamm_plan_create(C.byref(self._h), M, K, N, row_tile_begin, row_tile_count, device),
               "spamm_plan_create")
+
+    @classmethod
+    def _borrowed(cls, handle: int, device: int) -> "SpammPlan":
+        """A view of a plan that somebody else owns (a device of a `SpammGroup`): same methods, `close` does nothing."""
+        self = cls.__new__(cls)
+        self._lib = _lib.load()
+        self._h = C.c_void_p(handle)
+        self._owned = False
+        dims = [C.c_int() for _ in range(5)]
+        check(self._lib.spamm_plan_dims(self._h, *[C.byref(d) for d in dims]), "spamm_plan_dims")
+        self.M, self.K, self.N, self.row_tile_begin, self.row_tile_count = (d.value for d in dims)
+        self.Mp, self.Kp, self.Np = (-(-x // TILE) * TILE for x in (self.M, self.K, self.N))
+        self.device = device
+        return self
 
     # ---- lifetime
     def close(self) -> None:
         if getattr(self, "_h", None) and self._h.value:
-            self._lib.spamm_plan_destroy(self._h)
+            if self._owned:
+                self._lib.spamm_plan_destroy(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):
@@ -220,6 +236,32 @@ class SpammPlan:
     def norm_b_share_push(self, b_tile_begin: int, b_tile_count: int) -> None:
         check(self._lib.spamm_norm_b_share_push(self._h, b_tile_begin, b_tile_count), "spamm_norm_b_share_push")
 
+    def run_shared(self, tau: float, b_tile_begin: int, b_tile_count: int) -> None:
+        """One whole step of a plan that shares B's norm map with attached peers, in one call."""
+        check(self._lib.spamm_run_shared(self._h, float(tau), b_tile_begin, b_tile_count), "spamm_run_shared")
+
+    def norms_shared(self, b_tile_begin: int, b_tile_count: int) -> None:
+        """The first part of `run_shared`: both norm maps (this rank's rows of A, its share of B) in one launch and the
+        store of the share into the peers' maps."""
+        check(self._lib.spamm_norms_shared(self._h, b_tile_begin, b_tile_count), "spamm_norms_shared")
+
+    def upload_b_rows(self, b_rows, row_begin: int) -> None:
+        """Rows [row_begin, row_begin + len(b_rows)) of B into the plan's copy of B."""
+        rows = int(b_rows.shape[0])
+        check(self._lib.spamm_upload_b_rows(self._h, _host_ptr(b_rows, rows * self.N * 4), row_begin, rows),
+              "spamm_upload_b_rows")
+
+    def multiply_b_resident(self, a_rows, tau: float, out=None, b_ready_event: int = 0):
+        """`multiply` without the upload of B (the caller has assembled B on the GPU; `b_ready_event` is the handle of
+        a CUDA event after which it is complete, 0 if it already is)."""
+        if out is None:
+            out = np.empty((self.rows, self.N), dtype=np.float32)
+        st = SpammStats()
+        check(self._lib.spamm_multiply_b_resident(self._h, _host_ptr(a_rows, self.rows * self.K * 4),
+                                                  _host_ptr(out, self.rows * self.N * 4), float(tau),
+                                                  C.c_void_p(b_ready_event), C.byref(st)), "spamm_multiply_b_resident")
+        return out, st.as_dict()
+
     def compute_norm_a(self) -> None:
         check(self._lib.spamm_norm_a(self._h), "spamm_norm_a")
 
@@ -254,6 +296,50 @@ class SpammPlan:
 
     def sync(self) -> None:
         check(self._lib.spamm_sync(self._h), "spamm_sync")
+
+    def b_rows(self, rank: Optional[int] = None) -> Tuple[int, int]:
+        """(first row, number of rows) of B that rank `rank` (default: this one) brings to `multiply`."""
+        r = self.rank if rank is None else rank
+        if self.world == 1:
+            return 0, self.K
+        if self._share is not None:
+            b0, b1 = r * self._share * TILE, (r + 1) * self._share * TILE
+        else:                              # uneven: whole tile rows, the remainder to the first ranks
+            k_tiles = -(-self.K // TILE)
+            base, extra = divmod(k_tiles, self.world)
+            b0 = (r * base + min(r, extra)) * TILE
+            b1 = b0 + (base + (1 if r < extra else 0)) * TILE
+        return min(b0, self.K), min(b1, self.K) - min(b0, self.K)
+
+    def multiply(self, a_rows, b_rows, tau: float, out=None):
+        """Host matrices in and out on every rank, each over its own PCIe link: this rank's rows of A, its rows
+        `b_rows()` of B, its rows of C back (`out`, pinned for speed).  The shares of B are exchanged over NVLink
+        (NCCL all-gather, in place in the plans' copies of B) while the rows of A already go up; the path then runs in
+        chunks of rows with uploads, kernels and downloads overlapped.  Returns (rows of C, statistics of this rank).
+        The reference copies all of A and all of B to every device (cuSpAMM.cu:449-450)."""
+        if self.world == 1:
+            return self.plan.multiply(a_rows, b_rows, tau, out=out)
+        torch = self._torch
+        r0, _ = self.b_rows()
+        self.plan.upload_b_rows(b_rows, r0)
+        if self._stream is None:
+            self._stream = self.plan.torch_stream()
+        if self._gather_stream is None:
+            self._gather_stream = torch.cuda.Stream(priority=-5)
+            self._gather_done = torch.cuda.Event()
+        bfull = self.plan.as_tensor(BUF_B)
+        self._gather_stream.wait_stream(self._stream)
+        with torch.cuda.stream(self._gather_stream):
+            if self._share is not None:
+                rows = self._share * TILE
+                self._dist.all_gather_into_tensor(bfull, bfull[self.rank * rows:(self.rank + 1) * rows], group=self.group)
+            else:
+                for r in range(self.world):
+                    b0, n = self.b_rows(r)
+                    if n:
+                        self._dist.broadcast(bfull[b0:b0 + n], src=r, group=self.group)
+            self._gather_done.record(self._gather_stream)
+        return self.plan.multiply_b_resident(a_rows, tau, out=out, b_ready_event=self._gather_done.cuda_event)
 
     def run_timed(self, tau: float) -> dict:
         st = SpammStats()
@@ -363,20 +449,93 @@ class SpammPlan:
         return torch.cuda.ExternalStream(self.stream_ptr, device=f"cuda:{self.device}")
 
 
+class SpammGroup:
+    """Several GPUs driven by this one process: the reference's DEVICEDIM form (para.h:9, cuSpAMM.cu:404-451,470-537)
+    through the group entry points of the C ABI.  Whole host matrices in and out; the library splits C by row blocks,
+    uploads B by shares over every device's own PCIe link and exchanges shares and norm maps over NVLink."""
+
+    def __init__(self, M: int, K: int, N: int, devices: Optional[Sequence[int]] = None, n_devices: Optional[int] = None):
+        self._lib = _lib.load()
+        if devices is None:
+            devices = list(range(1 if n_devices is None else n_devices))
+        self.devices = [int(d) for d in devices]
+        self.M, self.K, self.N = M, K, N
+        self._h = C.c_void_p()
+        ids = (C.c_int * len(self.devices))(*self.devices)
+        check(self._lib.spamm_group_create(C.byref(self._h), M, K, N, len(self.devices), ids), "spamm_group_create")
+        self.plans = []
+        for i, d in enumerate(self.devices):
+            h = C.c_void_p()
+            check(self._lib.spamm_group_plan(self._h, i, C.byref(h)), "spamm_group_plan")
+            self.plans.append(SpammPlan._borrowed(h.value, d))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self._h.value:
+            for p in self.plans:
+                p.close()
+            self._lib.spamm_group_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def upload(self, a=None, b=None) -> None:
+        pa = _host_ptr(a, self.M * self.K * 4) if a is not None else 0
+        pb = _host_ptr(b, self.K * self.N * 4) if b is not None else 0
+        check(self._lib.spamm_group_upload(self._h, pa, pb), "spamm_group_upload")
+
+    def run(self, tau: float) -> None:
+        check(self._lib.spamm_group_run(self._h, float(tau)), "spamm_group_run")
+
+    def sync(self) -> None:
+        check(self._lib.spamm_group_sync(self._h), "spamm_group_sync")
+
+    def download_c(self, out=None):
+        if out is None:
+            out = np.empty((self.M, self.N), dtype=np.float32)
+        check(self._lib.spamm_group_download_c(self._h, _host_ptr(out, self.M * self.N * 4)), "spamm_group_download_c")
+        return out
+
+    def survivors(self) -> int:
+        s = C.c_int64()
+        check(self._lib.spamm_group_survivors(self._h, C.byref(s)), "spamm_group_survivors")
+        return int(s.value)
+
+    def multiply(self, a, b, tau: float, out=None):
+        if out is None:
+            out = np.empty((self.M, self.N), dtype=np.float32)
+        st = SpammStats()
+        check(self._lib.spamm_group_multiply(self._h, _host_ptr(a, self.M * self.K * 4), _host_ptr(b, self.K * self.N * 4),
+                                             _host_ptr(out, self.M * self.N * 4), float(tau), C.byref(st)),
+              "spamm_group_multiply")
+        return out, st.as_dict()
+
+
 class ShardedSpamm:
     """C sharded by row blocks over the ranks of a torch.distributed group (one process per GPU).
 
     Mirrors the reference's multi-device loop (cuSpAMM.cu:433-451, 470-537) with two changes the reference's
-    own layout invites: B is uploaded once and broadcast over NVLink instead of one host copy per device
-    (cuSpAMM.cu:449-450), and every rank computes only its share of B's norm map, the shares being all-gathered,
-    instead of each device recomputing all of it (cuSpAMM.cu:486).
+    own layout invites: B crosses PCIe once in all (by one rank and a broadcast, `distribute`, or in shares over
+    every rank's own link and an all-gather, `multiply`) instead of once per device (cuSpAMM.cu:449-450), and every
+    rank computes only its share of B's norm map, the shares being exchanged (`exchange="push"`: peer stores from
+    a small kernel, one library call per step; `exchange="nccl"`: an NCCL all-gather on a side stream), instead of
+    each device recomputing all of it (cuSpAMM.cu:486).
 
     `plan_factory(M, K, N, begin, count)` builds the per-rank plan (default: a `SpammPlan` on the current CUDA
     device); the tests pass a CPU stand-in to run the same orchestration over gloo.
     """
 
     def __init__(self, M: int, K: int, N: int, group=None, plan_factory=None, device: Optional[int] = None,
-                 exchange: str = "nccl", blocks=None):
+                 exchange: str = "push", blocks=None):
         import torch
         import torch.distributed as dist
 
@@ -385,6 +544,7 @@ class ShardedSpamm:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.M, self.K, self.N = M, K, N
+        self.Mp, self.Kp, self.Np = (-(-x // TILE) * TILE for x in (M, K, N))
         if blocks is None:
             blocks = row_blocks(-(-M // TILE), self.world)      # the reference's even split
         else:                                                   # e.g. from balanced_row_blocks
@@ -403,6 +563,8 @@ class ShardedSpamm:
         # equal shares of B's tile rows when they divide evenly, otherwise every rank computes the whole map
         self._share = (k_tiles // self.world) if (self.world > 1 and k_tiles % self.world == 0) else None
         self._nb = self._mine = self._stream = self._side = None
+        self._nb_ptr = 0
+        self._gather_stream = self._gather_done = None
         self._nccl = False
         # peer-to-peer exchange of B's norm-map shares (no collective in the step) when the plan offers it
         self._push = False
@@ -438,12 +600,14 @@ class ShardedSpamm:
         if self._share is None:
             self.plan.norms()
         elif self._push:
-            # this rank's share of B's map goes straight into every GPU's map from inside the norm kernel
-            self.plan.norm_b_share_push(self.rank * self._share, self._share)
-            self.plan.compute_norm_a()
-            self._clear_c_early()
+            # one library call for the whole step: the maps of this rank's rows of A and share of B in one launch, the
+            # share stored into every GPU's map by a small kernel, then lists (which wait for the shares), pack, multiply
+            self.plan.run_shared(tau, self.rank * self._share, self._share)
+            return
         else:
-            if self._nb is None:      # views and streams are built once: this runs every step
+            ptr = self.plan.buffer(BUF_NORM_B)[0] if hasattr(self.plan, "buffer") else 0
+            if self._nb is None or ptr != self._nb_ptr:      # views and streams are built once: this runs every step
+                self._nb_ptr = ptr                           # (again if the plan's current map of B has changed)
                 self._nb = self.plan.as_tensor(BUF_NORM_B)
                 self._mine = self._nb[self.rank * self._share:(self.rank + 1) * self._share]
                 self._nccl = self._dist.get_backend(self.group) == "nccl"
@@ -479,6 +643,50 @@ class ShardedSpamm:
         if f is not None:
             f()
 
+    def b_rows(self, rank: Optional[int] = None) -> Tuple[int, int]:
+        """(first row, number of rows) of B that rank `rank` (default: this one) brings to `multiply`."""
+        r = self.rank if rank is None else rank
+        if self.world == 1:
+            return 0, self.K
+        if self._share is not None:
+            b0, b1 = r * self._share * TILE, (r + 1) * self._share * TILE
+        else:                              # uneven: whole tile rows, the remainder to the first ranks
+            k_tiles = -(-self.K // TILE)
+            base, extra = divmod(k_tiles, self.world)
+            b0 = (r * base + min(r, extra)) * TILE
+            b1 = b0 + (base + (1 if r < extra else 0)) * TILE
+        return min(b0, self.K), min(b1, self.K) - min(b0, self.K)
+
+    def multiply(self, a_rows, b_rows, tau: float, out=None):
+        """Host matrices in and out on every rank, each over its own PCIe link: this rank's rows of A, its rows
+        `b_rows()` of B, its rows of C back (`out`, pinned for speed).  The shares of B are exchanged over NVLink
+        (NCCL all-gather, in place in the plans' copies of B) while the rows of A already go up; the path then runs in
+        chunks of rows with uploads, kernels and downloads overlapped.  Returns (rows of C, statistics of this rank).
+        The reference copies all of A and all of B to every device (cuSpAMM.cu:449-450)."""
+        if self.world == 1:
+            return self.plan.multiply(a_rows, b_rows, tau, out=out)
+        torch = self._torch
+        r0, _ = self.b_rows()
+        self.plan.upload_b_rows(b_rows, r0)
+        if self._stream is None:
+            self._stream = self.plan.torch_stream()
+        if self._gather_stream is None:
+            self._gather_stream = torch.cuda.Stream(priority=-5)
+            self._gather_done = torch.cuda.Event()
+        bfull = self.plan.as_tensor(BUF_B)
+        self._gather_stream.wait_stream(self._stream)
+        with torch.cuda.stream(self._gather_stream):
+            if self._share is not None:
+                rows = self._share * TILE
+                self._dist.all_gather_into_tensor(bfull, bfull[self.rank * rows:(self.rank + 1) * rows], group=self.group)
+            else:
+                for r in range(self.world):
+                    b0, n = self.b_rows(r)
+                    if n:
+                        self._dist.broadcast(bfull[b0:b0 + n], src=r, group=self.group)
+            self._gather_done.record(self._gather_stream)
+        return self.plan.multiply_b_resident(a_rows, tau, out=out, b_ready_event=self._gather_done.cuda_event)
+
     def run_timed(self, tau: float) -> dict:
         """One `run` with CUDA events between its parts (this rank's view, milliseconds); blocking."""
         torch = self._torch
@@ -489,8 +697,7 @@ class ShardedSpamm:
             self.plan.norms()
             ev[1].record(stream)
         elif self._push:
-            self.plan.norm_b_share_push(self.rank * self._share, self._share)
-            self.plan.compute_norm_a()
+            self.plan.norms_shared(self.rank * self._share, self._share)
             ev[1].record(stream)       # the wait for the other GPUs' shares is inside the list build
         else:
             self.plan.norms_share(self.rank * self._share, self._share)
@@ -545,7 +752,7 @@ class ShardedSpamm:
         equal = len({n for _, n in self.blocks}) == 1
         with self._on_stream():
             if self.rank == dst:
-                full = self._torch.empty((self.M, self.N), dtype=mine.dtype, device=mine.device)
+                full = self._torch.empty((self.Mp, self.Np), dtype=mine.dtype, device=mine.device)
                 parts = [full[b * TILE:(b + n) * TILE] for b, n in self.blocks]
             else:
                 full, parts = None, None

@@ -162,6 +162,17 @@ int spamm_peer_handles(spamm_plan *plan, void *out, size_t out_bytes);
 int spamm_peer_attach(spamm_plan *plan, int world, int rank, const void *all_handles);
 int spamm_norm_b_share_push(spamm_plan *plan, int b_tile_begin, int b_tile_count);
 /*
+ * One whole step of a GPU that shares the work on B's norm map with its peers (attached with spamm_peer_attach, or
+ * plans of one spamm_group), in a single call: one launch computes the norm maps of this plan's rows of A and of tile
+ * rows [b_tile_begin, b_tile_begin+b_tile_count) of B, a small kernel stores that share into every peer's map, then
+ * lists (which wait for the peers' shares), packing and multiply follow as in spamm_finish.  Asynchronous.  This is
+ * the per-device body of the reference's parallel region (cuSpAMM.cu:470-537) with B's map computed once instead of
+ * once per device (cuSpAMM.cu:486).
+ */
+int spamm_run_shared(spamm_plan *plan, float tau, int b_tile_begin, int b_tile_count);
+/* The first part of spamm_run_shared alone (the two norm maps and the store of the share); spamm_finish completes the step. */
+int spamm_norms_shared(spamm_plan *plan, int b_tile_begin, int b_tile_count);
+/*
  * Exercises the bounded device-side wait of the exchange on one GPU: a small kernel waits for arrival flags of
  * `senders` GPUs that nothing will ever set, gives up after limit_ms (1..5000) and reports it.  Returns
  * SPAMM_ERR_DEVICE_WAIT when the wait ran out as it should (the plan stays usable), SPAMM_OK if it did not.
@@ -178,7 +189,7 @@ int spamm_download_c(spamm_plan *plan, float *c_rows);
  * One call for the whole driver loop body with float host matrices in and out: upload, norms, lists, pack,
  * multiply, download; blocking.
  * a_rows / c_rows are this plan's row block, b is all of B.  stats may be NULL.
- * Blocks of more than about 64 MiB of A are processed in chunks of rows so that the upload of the next chunk, the
+ * Blocks of more than 16 MiB of A are processed in chunks of rows (16 to 64 MiB) so that the upload of the next chunk, the
  * kernels of the current one and the download of the previous one overlap (use pinned host memory for that); the
  * phases then interleave and only ms_device_total (the whole call, copies included), ms_h2d (B alone) and the
  * counts are reported.  After such a call spamm_gated_multiply needs a new spamm_build_lists.
@@ -187,8 +198,23 @@ int spamm_multiply(spamm_plan *plan, const float *a_rows, const float *b, float 
                    float tau, spamm_stats *stats);
 
 /*
- * Tile rows per chunk of the pipelined spamm_multiply (a multiple of 4; at most 64 chunks).  The default is about
- * 64 MiB of A per chunk.  A value >= the plan's row_tile_count turns the pipelining off.
+ * The two halves of spamm_multiply for callers that assemble B on the GPU themselves (several GPUs that each upload a
+ * share of B over their own PCIe link and exchange the shares over NVLink; the reference copies all of B to every
+ * device, cuSpAMM.cu:449-450).
+ *   spamm_upload_b_rows        rows [row_begin, row_begin+rows) of B (leading dimension N) into the plan's copy of B,
+ *                              asynchronous on the plan's stream;
+ *   spamm_multiply_b_resident  spamm_multiply without the upload of B: the rows of A go up, the path runs and the
+ *                              rows of C come down, pipelined in chunks as in spamm_multiply.  b_ready_event (a
+ *                              cudaEvent_t, may be NULL) is an event after which B is complete in the plan's buffer;
+ *                              the uploads of A do not wait for it, the first kernel that reads B does.
+ */
+int spamm_upload_b_rows(spamm_plan *plan, const float *b_rows, int row_begin, int rows);
+int spamm_multiply_b_resident(spamm_plan *plan, const float *a_rows, float *c_rows, float tau, void *b_ready_event,
+                              spamm_stats *stats);
+
+/*
+ * Tile rows per chunk of the pipelined spamm_multiply (a multiple of 4; at most 64 chunks).  The default is an eighth
+ * of the block, between 16 and 64 MiB of A.  A value >= the plan's row_tile_count turns the pipelining off.
  */
 int spamm_plan_set_chunk_tiles(spamm_plan *plan, int tiles);
 
@@ -273,6 +299,43 @@ int spamm_device_buffer(spamm_plan *plan, int which, void **d_ptr, size_t *bytes
 /* The plan's cudaStream_t, as an opaque pointer. */
 int spamm_stream(spamm_plan *plan, void **stream);
 int spamm_plan_dims(spamm_plan *plan, int *M, int *K, int *N, int *row_tile_begin, int *row_tile_count);
+
+/* ---------------------------------------------------------------- several GPUs, one process ------- */
+
+/*
+ * The reference drives DEVICEDIM GPUs from one process (para.h:9): per-device plans and full replicas of A and B
+ * (cuSpAMM.cu:404-451), one host thread per device in the timed region (cuSpAMM.cu:470-537), every device computing
+ * all of B's norm map (cuSpAMM.cu:486), no gather of C.  A spamm_group is that, for one host thread and with the
+ * redundancy removed: device d owns C tile rows [d*T/G, (d+1)*T/G) (boundaries on multiples of 4 tile rows), only its
+ * rows of A are uploaded to it, every device uploads 1/G of B over its own PCIe link and the shares are exchanged with
+ * peer-to-peer copies over NVLink, every device computes 1/G of B's norm map per step and stores it into the other
+ * devices' maps (plain peer stores; the list builder waits, at most 2 s, for all shares), and every device copies its
+ * rows of C into its slice of the host result.  Needs peer access between all devices of the group
+ * (SPAMM_ERR_UNSUPPORTED otherwise); n_devices 1..8; device_ids NULL means 0..n_devices-1.  K/32 need not divide
+ * by n_devices (the shares of B then differ by one tile row).  Not thread-safe; one host thread drives all devices.
+ */
+typedef struct spamm_group spamm_group;
+int spamm_group_create(spamm_group **out, int M, int K, int N, int n_devices, const int *device_ids);
+int spamm_group_destroy(spamm_group *group);
+int spamm_group_size(spamm_group *group);
+/* Plan of device i of the group (owned by the group), for the read-backs above and for spamm_plan_dims. */
+int spamm_group_plan(spamm_group *group, int i, spamm_plan **plan);
+/* Host->device: the rows of A to their owners, B by shares + exchange.  Either may be NULL.  Asynchronous. */
+int spamm_group_upload(spamm_group *group, const float *a, const float *b);
+/* One step of the timed region on every device (spamm_run_shared per device; spamm_run for a group of one). */
+int spamm_group_run(spamm_group *group, float tau);
+/* Waits for every device; the first failure of any device is returned. */
+int spamm_group_sync(spamm_group *group);
+/* Device->host: every device's rows of C into c (M x N, leading dimension N); blocking. */
+int spamm_group_download_c(spamm_group *group, float *c);
+/* Sum of the devices' surviving products of the last step; blocking. */
+int spamm_group_survivors(spamm_group *group, int64_t *survivors);
+/*
+ * Host matrices in and out on all devices: B by shares and exchange, then per device the pipelined upload of its rows
+ * of A, the path, and the download of its rows of C (spamm_multiply_b_resident); blocking.  stats (may be NULL)
+ * receives the sums of the counts and, as ms_device_total, the slowest device's time.
+ */
+int spamm_group_multiply(spamm_group *group, const float *a, const float *b, float *c, float tau, spamm_stats *stats);
 
 /* ---------------------------------------------------------------- kernels on caller memory -------- */
 /* `stream` is a cudaStream_t passed as void*; all launches are asynchronous. */

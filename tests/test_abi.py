@@ -116,3 +116,20 @@ def test_macro_tile_order_is_a_permutation(lib):
         order = np.full(n, -1, dtype=np.int32)
         assert lib.spamm_macro_tile_order(row_tiles, n_tiles, order.ctypes.data) == 0
         assert np.array_equal(np.sort(order), np.arange(n))
+
+
+def test_group_argument_validation_needs_no_gpu(lib):
+    g = C.c_void_p()
+    ids = (C.c_int * 2)(0, 0)
+    assert lib.spamm_group_create(None, 64, 64, 64, 1, None) == 1
+    assert lib.spamm_group_create(C.byref(g), 64, 64, 64, 0, None) == 1       # no device
+    assert lib.spamm_group_create(C.byref(g), 64, 64, 64, 9, None) == 1       # more than 8
+    assert lib.spamm_group_create(C.byref(g), 64, 0, 64, 1, None) == 1        # empty matrix
+    assert lib.spamm_group_create(C.byref(g), 64, 64, 64, 2, ids) == 1        # the same device twice
+    assert lib.spamm_group_destroy(None) == 0
+    assert lib.spamm_group_size(None) == 0
+    assert lib.spamm_group_run(None, 0.0) == 1
+    assert lib.spamm_group_multiply(None, None, None, None, 0.0, None) == 1
+    assert lib.spamm_run_shared(None, 0.0, 0, 1) == 1
+    assert lib.spamm_upload_b_rows(None, None, 0, 0) == 1
+    assert lib.spamm_multiply_b_resident(None, None, None, 0.0, None, None) == 1
