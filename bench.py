@@ -3,7 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--n SIZE] [--tau TAU]
                     [--workload exp|alg|lattice|dense] [--precision half|split] [--partition auto|even|balanced]
-                    [--exchange push|nccl] [--no-sweep] [--no-cpu] [--no-ref-kernels]
+                    [--exchange push|nccl] [--multiply-mode auto|one_sm|gated_pairs] [--no-sweep] [--no-cpu]
+                    [--no-ref-kernels]
 
 One "step" is one pass of the reference's timed region (cuSpAMM.cu:458-546) over matrices that are already
 resident in HBM.  The default workload is the configuration the headline metric is quoted on: N=16384, exponential
@@ -348,6 +349,8 @@ def run_ours(args):
         sh = ShardedSpamm(n, n, n, exchange=args.exchange, blocks=blocks)
         if args.precision != "half":
             sh.plan.set_precision(args.precision)
+        if args.multiply_mode != "auto":
+            sh.plan.set_multiply_mode(args.multiply_mode)
         a_t, a_np = pinned((sh.plan.rows, n))
         generate_into(a_np, SEED_A, sh.row_tile_begin * TILE, n)
         return sh, a_t, a_np
@@ -787,6 +790,8 @@ def main():
                     help="skip timing the reference's own kernels (N=8192) beside the library")
     ap.add_argument("--precision", default="half", choices=["half", "split"],
                     help="half: the metric's configuration; split: the float-accuracy mode (three tensor-core passes)")
+    ap.add_argument("--multiply-mode", default="auto", choices=["auto", "one_sm", "gated_pairs"],
+                    help="which multiply kernels may run (auto: chosen from the counters of the previous step)")
     ap.add_argument("--partition", default="auto", choices=["auto", "even", "balanced"],
                     help="row blocks of C per GPU: even (the reference's), or moved so that the surviving products "
                          "are spread evenly (auto: only when that lowers the largest block's work by more than 3 %%)")

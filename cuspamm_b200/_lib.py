@@ -46,6 +46,7 @@ SIGNATURES = {
     "spamm_upload": (_i, [_vp, _vp, _vp]),
     "spamm_plan_set_chunk_tiles": (_i, [_vp, _i]),
     "spamm_plan_set_pack_mode": (_i, [_vp, _i]),
+    "spamm_plan_set_multiply_mode": (_i, [_vp, _i]),
     "spamm_clear_c_early": (_i, [_vp]),
     "spamm_plan_set_precision": (_i, [_vp, _i]),
     "spamm_norms": (_i, [_vp]),

@@ -14,7 +14,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libspamm.so"
-SOURCES = ["norm_map.cu", "skip_lists.cu", "pack_half.cu", "gated_multiply.cu", "gated_multiply_pair.cu", "plan.cu", "group.cu", "extras.cu",
+SOURCES = ["norm_map.cu", "skip_lists.cu", "pack_half.cu", "gated_multiply.cu", "gated_multiply_pair.cu", "gated_multiply_gpair.cu", "plan.cu", "group.cu", "extras.cu",
            "generators.cpp"]
 HEADERS = [CSRC / "common.cuh", CSRC / "tc_utils.cuh", CSRC / "plan.cuh", PKG_DIR.parent / "include" / "spamm.h"]
 

@@ -72,7 +72,11 @@ int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_ti
 int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                           const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                           spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                          int64_t ldc, bool reset_queues, bool try_pairs, int mode, cudaStream_t stream);
+                          int64_t ldc, bool reset_queues, int pairs, int mode, cudaStream_t stream);
+// `pairs` of gated_multiply_launch: which kernel on pairs of SMs runs before the one-SM kernel
+constexpr int GM_PAIRS_NONE = 0;    // none
+constexpr int GM_PAIRS_DENSE = 1;   // dense macro tiles with dense neighbours (gated_multiply_pair.cu); a no-op below half dense
+constexpr int GM_PAIRS_GATED = 2;   // every pair of macro-tile rows, gated (gated_multiply_gpair.cu)
 // `mode` of gated_multiply_launch, a sum of:
 constexpr int GM_C_ZEROED = 1;      // C was cleared beforehand (or holds a partial result): macro tiles without steps are left alone
 constexpr int GM_ACCUMULATE = 2;    // the products are added to what C holds instead of replacing it
@@ -83,6 +87,10 @@ constexpr float SPLIT_LOW_SCALE = 2048.0f;
 int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const int32_t *d_step_counts,
                                spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
                                int64_t ldc, cudaStream_t stream);
+
+int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
+                                const int32_t *d_step_counts, spamm_list_scalars *d_scalars, int row_tiles, int k_tiles,
+                                int n_tiles, float *d_c, int64_t ldc, int mode, cudaStream_t stream);
 
 #define SPAMM_CUDA_TRY(call)                                                    \
     do {                                                                        \

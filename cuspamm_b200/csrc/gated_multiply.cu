@@ -156,9 +156,13 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
     tc_fence_after();
 
     // Dense macro tiles that have a dense vertical neighbour belong to the paired (two-SM) kernel, which runs first
-    // on the stream whenever at least half of the macro tiles are dense; this kernel leaves them alone.
-    const bool pair_active = pairs_launched && mi_n >= 2 && sc->dense_count * 2u >= n_mt;
+    // on the stream whenever at least half of the macro tiles are dense; this kernel leaves them alone.  When the
+    // gated two-SM kernel ran instead, it took every pair of macro-tile rows, and only the last row of an odd count
+    // is left for this one.
+    const bool gated_pairs = pairs_launched == GM_PAIRS_GATED && mi_n >= 2;
+    const bool pair_active = gated_pairs || (pairs_launched == GM_PAIRS_DENSE && mi_n >= 2 && sc->dense_count * 2u >= n_mt);
     auto pair_owned = [&](int mt, int raw_count) -> bool {
+        if (gated_pairs) return mt / mj_n < (mi_n & ~1);
         if (!pair_active || !step_list_dense(raw_count)) return false;
         const int mi = mt / mj_n, partner = mi ^ 1;
         return partner < mi_n && step_list_dense(step_counts[partner * mj_n + (mt % mj_n)]);
@@ -537,18 +541,20 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
                                         int k_tiles, int n_tiles, float *d_c, int64_t ldc, void *stream)
 {
     return spamm::gated_multiply_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_order, d_busy_list, d_scalars,
-                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, true, 0, (cudaStream_t)stream);
+                                        row_tiles, k_tiles, n_tiles, d_c, ldc, true, spamm::GM_PAIRS_DENSE, 0,
+                                        (cudaStream_t)stream);
 }
 
 int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                                  const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                                  spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                                 int64_t ldc, bool reset_queues, bool try_pairs, int mode, cudaStream_t stream)
+                                 int64_t ldc, bool reset_queues, int pairs, int mode, cudaStream_t stream)
 {
     using namespace spamm;
     // adding to C only makes sense where C is not overwritten with zeros, and never through the paired kernel
     if (mode < 0 || mode > (GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND) ||
-        ((mode & GM_ACCUMULATE) && (!(mode & GM_C_ZEROED) || try_pairs)) ||
+        pairs < GM_PAIRS_NONE || pairs > GM_PAIRS_GATED ||
+        ((mode & GM_ACCUMULATE) && (!(mode & GM_C_ZEROED) || pairs == GM_PAIRS_DENSE)) ||
         ((mode & GM_LOW_OPERAND) && !(mode & GM_ACCUMULATE)))
         return SPAMM_ERR_INVALID;
     if (!d_half_a || !d_half_b || !d_steps || !d_step_counts || !d_busy_list || !d_scalars || !d_c || row_tiles < 0 ||
@@ -582,15 +588,21 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
     if (reset_queues) SPAMM_CUDA_TRY(cudaMemsetAsync(&d_scalars->queue_busy, 0, 3 * sizeof(unsigned int), stream));
     // dense macro tiles with a dense vertical neighbour go to pairs of SMs first (a no-op below half dense);
     // a caller that knows the lists are sparse can save the launch
-    if (try_pairs) {
+    if (pairs == GM_PAIRS_DENSE) {
         int st = gated_multiply_pair_launch(d_half_a, d_half_b, d_step_counts, d_scalars, row_tiles, k_tiles, n_tiles,
                                             d_c, ldc, stream);
         if (st) return st;
+    } else if (pairs == GM_PAIRS_GATED) {
+        int st = gated_multiply_gpair_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_scalars, row_tiles, k_tiles,
+                                             n_tiles, d_c, ldc, mode, stream);
+        if (st) return st;
+        // an even number of macro-tile rows: nothing is left for the one-SM kernel
+        if (ceil_div(row_tiles, MT_R) >= 2 && ceil_div(row_tiles, MT_R) % 2 == 0) return SPAMM_OK;
     }
     const int grid = (int)(n_mt < sm_count ? n_mt : sm_count);
     gated_multiply_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, stream>>>(
         static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts,
-        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, try_pairs ? 1 : 0, mode);
+        d_order, d_busy_list, d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, pairs, mode);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -102,6 +102,17 @@ int read_scalars(spamm_plan *p)
     unsigned long long dense = 0;
     for (int c = 0; c < p->active_scalars; c++) dense += p->h_scalars[c].dense_count;
     p->dense_hint = (dense * 2 >= p->n_mt() && p->n_mt() > 0) ? 1 : 0;
+    // and whether they were long lists in most macro tiles (at least 1024 surviving products per macro tile that has
+    // any, i.e. 32 full steps' worth): the traffic from L2 into the SMs then bounds the multiply, and the gated kernel
+    // on pairs of SMs, which shares the tiles of B between two macro tiles, is the faster one
+    {
+        unsigned long long busy = 0, surv = 0;
+        for (int c = 0; c < p->active_scalars; c++) {
+            busy += p->h_scalars[c].busy_count;
+            surv += p->h_scalars[c].survivors;
+        }
+        p->gpair_hint = (p->have_lists && busy * 2 >= p->n_mt() && busy > 0 && surv >= 1024ull * busy) ? 1 : 0;
+    }
     // and whether few macro tiles had steps: the next step then clears C with a memset on the second stream while
     // the lists are built and the tiles converted (kernels that leave the memory system idle), and its multiply
     // writes only the macro tiles that have steps
@@ -139,6 +150,16 @@ int64_t total_survivors(const spamm_plan *p)
 
 extern "C" {
 static int build_lists_impl(spamm_plan *p, float tau, bool whole_step);
+}
+
+// Which kernel on pairs of SMs runs before the one-SM multiply kernel (a wrong guess costs speed, never correctness).
+static int pairs_choice(const spamm_plan *p)
+{
+    if (p->multiply_mode == SPAMM_MULTIPLY_ONE_SM) return GM_PAIRS_NONE;
+    if (p->multiply_mode == SPAMM_MULTIPLY_GATED_PAIRS) return GM_PAIRS_GATED;
+    if (p->dense_hint == 1) return GM_PAIRS_DENSE;
+    if (p->gpair_hint == 1) return GM_PAIRS_GATED;
+    return p->dense_hint != 0 ? GM_PAIRS_DENSE : GM_PAIRS_NONE;      // unknown yet: the dense kernel checks by itself
 }
 
 // (Re)builds the macro-tile orders for the chunk shapes of the pipelined spamm_multiply.
@@ -182,6 +203,14 @@ int spamm_plan_set_precision(spamm_plan *p, int precision)
         p->packed_all = false;      // the norm pass converts high parts only: spamm_pack must run
     }
     p->precision = precision;
+    return SPAMM_OK;
+}
+
+int spamm_plan_set_multiply_mode(spamm_plan *p, int mode)
+{
+    if (!p || (mode != SPAMM_MULTIPLY_AUTO && mode != SPAMM_MULTIPLY_ONE_SM && mode != SPAMM_MULTIPLY_GATED_PAIRS))
+        return SPAMM_ERR_INVALID;
+    p->multiply_mode = mode;
     return SPAMM_OK;
 }
 
@@ -649,7 +678,7 @@ int spamm_gated_multiply(spamm_plan *p)
         p->c_zero_pending = false;      // consumed: a second multiply on the same lists writes all of C itself
         int st = gated_multiply_launch(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
                                        p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N,
-                                       !p->queues_clean, p->dense_hint != 0, zeroed ? GM_C_ZEROED : 0, p->stream);
+                                       !p->queues_clean, pairs_choice(p), zeroed ? GM_C_ZEROED : 0, p->stream);
         p->queues_clean = false;
         if (st) return st;
         p->launches++;
@@ -659,7 +688,8 @@ int spamm_gated_multiply(spamm_plan *p)
             for (int pass = 0; pass < 2; pass++) {
                 st = gated_multiply_launch(pass == 0 ? p->d_half_a : p->d_low_a, pass == 0 ? p->d_low_b : p->d_half_b,
                                            p->d_steps, p->d_step_counts, p->d_order, p->d_busy, p->scalars(),
-                                           p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, true, false,
+                                           p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, true,
+                                           pairs_choice(p) == GM_PAIRS_GATED ? GM_PAIRS_GATED : GM_PAIRS_NONE,
                                            GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, p->stream);
                 if (st) return st;
                 p->launches++;
@@ -805,13 +835,14 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
         return st;
     if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, p->dense_hint != 0, 0, stream)))
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, pairs_choice(p), 0, stream)))
         return st;
     for (int pass = 0; split && pass < 2; pass++) {
         if ((st = gated_multiply_launch(pass == 0 ? half_a : low_a, pass == 0 ? p->d_low_b : p->d_half_b,
                                         p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0, d_order,
                                         p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                        p->d_c + (size_t)t0 * TILE * p->N, p->N, true, false,
+                                        p->d_c + (size_t)t0 * TILE * p->N, p->N, true,
+                                        pairs_choice(p) == GM_PAIRS_GATED ? GM_PAIRS_GATED : GM_PAIRS_NONE,
                                         GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, stream)))
             return st;
         p->launches++;

@@ -81,47 +81,46 @@ int main(int argc, char **argv)
     else { fprintf(stderr, "unknown matrix kind %s\n", matrix.c_str()); return 2; }
     if (st) return fail("generator", st);
 
-    std::vector<spamm_plan *> plan(devices, nullptr);
-    std::vector<int> begin(devices), count(devices);
-    for (int d = 0, b = 0; d < devices; d++) {          // device d owns tile rows [d*T/G, (d+1)*T/G), cuSpAMM.cu:503
-        begin[d] = b;
-        count[d] = (d == devices - 1) ? row_tiles - b : row_tiles / devices;
-        b += count[d];
-        if ((st = spamm_plan_create(&plan[d], M, K, N, begin[d], count[d], d))) return fail("spamm_plan_create", st);
-        if (split && (st = spamm_plan_set_precision(plan[d], SPAMM_PRECISION_SPLIT)))
-            return fail("spamm_plan_set_precision", st);
-        if ((st = spamm_upload(plan[d], h_A + (size_t)begin[d] * 32 * K, h_B))) return fail("spamm_upload", st);
-    }
+    // all devices through one group: every device owns a block of C tile rows (cuSpAMM.cu:503), uploads its rows of A
+    // and its share of B, and computes its share of B's norm map in every step
+    spamm_group *group = nullptr;
+    if ((st = spamm_group_create(&group, M, K, N, devices, nullptr))) return fail("spamm_group_create", st);
+    if (split)
+        for (int d = 0; d < devices; d++) {
+            spamm_plan *pl = nullptr;
+            if ((st = spamm_group_plan(group, d, &pl)) || (st = spamm_plan_set_precision(pl, SPAMM_PRECISION_SPLIT)))
+                return fail("spamm_plan_set_precision", st);
+        }
+    if ((st = spamm_group_upload(group, h_A, h_B))) return fail("spamm_group_upload", st);
     float norm = (float)tau;
     if (tune > 0) {                                     // TUNINGFLAG, main.h:35-38, cuSpAMM.cu:513-515
         double rate = 0;
         int it = 0;
-        if ((st = spamm_norms(plan[0]))) return fail("spamm_norms", st);
-        if ((st = spamm_tune_tau(plan[0], tune, 20, 0.01, &norm, &rate, &it))) return fail("spamm_tune_tau", st);
+        spamm_plan *pl = nullptr;
+        // as the reference: tuned on the first device's block of rows (every device would find its own value there)
+        if ((st = spamm_group_run(group, norm)) || (st = spamm_group_sync(group))) return fail("spamm_group_run", st);
+        if ((st = spamm_group_plan(group, 0, &pl))) return fail("spamm_group_plan", st);
+        if ((st = spamm_tune_tau(pl, tune, 20, 0.01, &norm, &rate, &it))) return fail("spamm_tune_tau", st);
         printf("tuned Norm=%g valid ratio=%f after %d passes\n", norm, rate, it);
     }
     double sum = 0;
     for (int i = 0; i < iters; i++) {
-        for (int d = 0; d < devices; d++) if ((st = spamm_sync(plan[d]))) return fail("spamm_sync", st);
+        if ((st = spamm_group_sync(group))) return fail("spamm_group_sync", st);
         const auto t0 = std::chrono::steady_clock::now();
-        for (int d = 0; d < devices; d++) if ((st = spamm_run(plan[d], norm))) return fail("spamm_run", st);
-        for (int d = 0; d < devices; d++) if ((st = spamm_sync(plan[d]))) return fail("spamm_sync", st);
+        if ((st = spamm_group_run(group, norm))) return fail("spamm_group_run", st);
+        if ((st = spamm_group_sync(group))) return fail("spamm_group_sync", st);
         const double el = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         if (i >= warmup) sum += el;
     }
     int64_t survivors = 0;
-    for (int d = 0; d < devices; d++) {
-        int64_t s = 0;
-        if ((st = spamm_get_counts(plan[d], nullptr, &s))) return fail("spamm_get_counts", st);
-        survivors += s;
-        if ((st = spamm_download_c(plan[d], h_C + (size_t)begin[d] * 32 * N))) return fail("spamm_download_c", st);
-    }
+    if ((st = spamm_group_survivors(group, &survivors))) return fail("spamm_group_survivors", st);
+    if ((st = spamm_group_download_c(group, h_C))) return fail("spamm_group_download_c", st);
     const double t = sum / (iters - warmup);
     const double total = (double)(Mp / 32) * (Kp / 32) * (Np / 32);
     printf("valid mul=%lld, simple mul=%.0f, rate=%f%%\n", (long long)survivors, total, 100.0 * survivors / total);
     printf("SpAMM time=%fs\n", t);
     printf("executed TFLOP/s=%f\n", 65536.0 * survivors / t / 1e12);
-    for (int d = 0; d < devices; d++) spamm_plan_destroy(plan[d]);
+    spamm_group_destroy(group);
     cudaFreeHost(h_A); cudaFreeHost(h_B); cudaFreeHost(h_C);
     return 0;
 }

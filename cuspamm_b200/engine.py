@@ -210,6 +210,14 @@ class SpammPlan:
             raise ValueError(f"pack mode must be one of {sorted(modes)}")
         check(self._lib.spamm_plan_set_pack_mode(self._h, modes[mode]), "spamm_plan_set_pack_mode")
 
+    def set_multiply_mode(self, mode: str) -> None:
+        """Which multiply kernels may run: "auto" (default, by the counters of the previous step), "one_sm", or
+        "gated_pairs" (the gated kernel on pairs of SMs for every pair of macro-tile rows).  Same results."""
+        modes = {"auto": 0, "one_sm": 1, "gated_pairs": 2}
+        if mode not in modes:
+            raise ValueError(f"multiply mode must be one of {sorted(modes)}")
+        check(self._lib.spamm_plan_set_multiply_mode(self._h, modes[mode]), "spamm_plan_set_multiply_mode")
+
     # ---- the driver steps
     def upload(self, a_rows=None, b=None) -> None:
         pa = _host_ptr(a_rows, self.rows * self.K * 4) if a_rows is not None else 0

@@ -258,6 +258,20 @@ int spamm_clear_c_early(spamm_plan *plan);
 enum { SPAMM_PACK_AUTO = 0, SPAMM_PACK_LISTED = 1, SPAMM_PACK_ALL = 2 };
 int spamm_plan_set_pack_mode(spamm_plan *plan, int mode);
 
+/*
+ * Which multiply kernels spamm_gated_multiply may use.  Results are the same in every mode (up to the order of the float
+ * additions inside the tensor cores).
+ *   SPAMM_MULTIPLY_AUTO         (default) by the counters of the plan's previous step: mostly dense macro tiles go to
+ *                               pairs of SMs ungated; long lists in most macro tiles go to the gated kernel on pairs of
+ *                               SMs (two vertically adjacent macro tiles share the tiles of B they load: a third less
+ *                               traffic from L2 into the SMs, which is what bounds such workloads); everything else to
+ *                               the one-SM kernel;
+ *   SPAMM_MULTIPLY_ONE_SM       the one-SM kernel only;
+ *   SPAMM_MULTIPLY_GATED_PAIRS  the gated kernel on pairs of SMs for every pair of macro-tile rows.
+ */
+enum { SPAMM_MULTIPLY_AUTO = 0, SPAMM_MULTIPLY_ONE_SM = 1, SPAMM_MULTIPLY_GATED_PAIRS = 2 };
+int spamm_plan_set_multiply_mode(spamm_plan *plan, int mode);
+
 /* Same as spamm_run but records per-phase events; blocking.  Inputs must already be resident. */
 int spamm_run_timed(spamm_plan *plan, float tau, spamm_stats *stats);
 

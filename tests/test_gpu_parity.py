@@ -502,3 +502,59 @@ def test_split_precision_on_small_magnitudes(oracle):
         p.sync()
         assert p.counts()[1] == S
         assert rel_fro(p.download_c(), C_exact) <= 1e-5
+
+
+def _lattice_like(M, K, N, seed):
+    """Matrices whose lists are long and partly full: a smooth decay away from the diagonal times random magnitudes,
+    so that neighbouring tiles keep similar but not identical sets of k."""
+    rng = np.random.default_rng(seed)
+    i = np.arange(M)[:, None] / M
+    k = np.arange(K)[None, :] / K
+    A = (np.exp(-6.0 * np.abs(i - k)) * rng.uniform(0.2, 1.0, (M, K)) * rng.choice([-1.0, 1.0], (M, K))).astype(np.float32)
+    k2 = np.arange(K)[:, None] / K
+    j = np.arange(N)[None, :] / N
+    B = (np.exp(-6.0 * np.abs(k2 - j)) * rng.uniform(0.2, 1.0, (K, N)) * rng.choice([-1.0, 1.0], (K, N))).astype(np.float32)
+    return A, B
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (512, 768, 512), (384, 512, 800), (160, 96, 416), (1024, 2048, 1024)])
+def test_gated_kernel_on_pairs_of_sms(oracle, shape):
+    """The gated two-SM kernel (two vertically adjacent macro tiles share the tiles of B), forced for every pair of
+    macro-tile rows: same norm maps and lists, C within tolerance, for full, partial and odd numbers of macro-tile rows
+    and columns, at thresholds from 'everything' to 'nothing'; a repeat on the same lists; the float-accuracy mode."""
+    from cuspamm_b200 import SpammPlan
+
+    M, K, N = shape
+    A, B = _lattice_like(M, K, N, seed=M + N)
+    prods = oracle.norm_map(A)[:, :, None] * oracle.norm_map(B)[None]
+    taus = [0.0, float(np.quantile(prods, 0.3)), float(np.quantile(prods, 0.7)), float(np.quantile(prods, 0.97)),
+            float(prods.max()) * 2]
+    with SpammPlan(M, K, N) as p:
+        p.set_multiply_mode("gated_pairs")
+        p.upload(A, B)
+        for tau in taus:
+            C_ref, S, _, _, counts = oracle.spamm(A, B, tau, want_maps=True)
+            p.run(tau)
+            p.sync()
+            got_counts, got_s = p.counts()
+            assert got_s == S and np.array_equal(got_counts, counts)
+            C = p.download_c()
+            assert rel_fro(C, C_ref) <= C_TOL, (tau, rel_fro(C, C_ref))
+            empty = counts == 0
+            if empty.any():
+                assert not C.reshape(M // 32, 32, N // 32, 32).transpose(0, 2, 1, 3)[empty].any()
+            p.gated_multiply()                       # again on the same lists
+            p.sync()
+            assert np.array_equal(p.download_c(), C)
+        tau = taus[2]
+        C_exact, S = oracle.spamm_exact(A, B, tau)
+        p.set_precision("split")
+        p.run(tau)
+        p.sync()
+        assert p.counts()[1] == S and rel_fro(p.download_c(), C_exact) <= 1e-5
+        p.set_precision("half")
+        p.set_multiply_mode("one_sm")
+        C_ref, S = oracle.spamm(A, B, tau)
+        p.run(tau)
+        p.sync()
+        assert rel_fro(p.download_c(), C_ref) <= C_TOL
