@@ -72,7 +72,8 @@ int pack_half_launch(const float *d_a, const float *d_b, int row_tiles, int k_ti
 int gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                           const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                           spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                          int64_t ldc, bool reset_queues, int pairs, int mode, cudaStream_t stream);
+                          int64_t ldc, bool reset_queues, int pairs, int mode, cudaStream_t stream,
+                          const struct GpairArgs *gpair = nullptr);
 // `pairs` of gated_multiply_launch: which kernel on pairs of SMs runs before the one-SM kernel
 constexpr int GM_PAIRS_NONE = 0;    // none
 constexpr int GM_PAIRS_DENSE = 1;   // dense macro tiles with dense neighbours (gated_multiply_pair.cu); a no-op below half dense
@@ -88,8 +89,18 @@ int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const
                                spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
                                int64_t ldc, cudaStream_t stream);
 
-int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
-                                const int32_t *d_step_counts, spamm_list_scalars *d_scalars, int row_tiles, int k_tiles,
+// What the gated two-SM kernel needs beyond the lists: it derives its own per-pair records from the norm maps.
+struct GpairArgs {
+    const float *norm_a, *norm_b;   // the maps the lists were built from (norm_a: this block of rows)
+    float tau;                      // and the threshold
+    const void *chunk_max;          // the list builder's scratch (chunk maxima), still holding that build's values
+    void *scratch;                  // gated_multiply_gpair_scratch_bytes(...) bytes, 16-byte aligned
+    bool build;                     // the records are not there yet (first multiply on these lists)
+};
+size_t gated_multiply_gpair_scratch_bytes(int row_tiles, int k_tiles, int n_tiles);
+int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, const float *d_norm_a, const float *d_norm_b,
+                                float tau, const void *d_chunk_max, const int32_t *d_step_counts, void *d_scratch,
+                                bool build_records, spamm_list_scalars *d_scalars, int row_tiles, int k_tiles,
                                 int n_tiles, float *d_c, int64_t ldc, int mode, cudaStream_t stream);
 
 #define SPAMM_CUDA_TRY(call)                                                    \

@@ -548,12 +548,13 @@ extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half
 int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
                                  const int32_t *d_step_counts, const int32_t *d_order, const int32_t *d_busy_list,
                                  spamm_list_scalars *d_scalars, int row_tiles, int k_tiles, int n_tiles, float *d_c,
-                                 int64_t ldc, bool reset_queues, int pairs, int mode, cudaStream_t stream)
+                                 int64_t ldc, bool reset_queues, int pairs, int mode, cudaStream_t stream,
+                                 const GpairArgs *gpair)
 {
     using namespace spamm;
     // adding to C only makes sense where C is not overwritten with zeros, and never through the paired kernel
     if (mode < 0 || mode > (GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND) ||
-        pairs < GM_PAIRS_NONE || pairs > GM_PAIRS_GATED ||
+        pairs < GM_PAIRS_NONE || pairs > GM_PAIRS_GATED || (pairs == GM_PAIRS_GATED && !gpair) ||
         ((mode & GM_ACCUMULATE) && (!(mode & GM_C_ZEROED) || pairs == GM_PAIRS_DENSE)) ||
         ((mode & GM_LOW_OPERAND) && !(mode & GM_ACCUMULATE)))
         return SPAMM_ERR_INVALID;
@@ -593,7 +594,8 @@ int spamm::gated_multiply_launch(const void *d_half_a, const void *d_half_b, con
                                             d_c, ldc, stream);
         if (st) return st;
     } else if (pairs == GM_PAIRS_GATED) {
-        int st = gated_multiply_gpair_launch(d_half_a, d_half_b, d_steps, d_step_counts, d_scalars, row_tiles, k_tiles,
+        int st = gated_multiply_gpair_launch(d_half_a, d_half_b, gpair->norm_a, gpair->norm_b, gpair->tau, gpair->chunk_max,
+                                             d_step_counts, gpair->scratch, gpair->build, d_scalars, row_tiles, k_tiles,
                                              n_tiles, d_c, ldc, mode, stream);
         if (st) return st;
         // an even number of macro-tile rows: nothing is left for the one-SM kernel

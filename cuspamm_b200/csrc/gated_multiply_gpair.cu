@@ -7,16 +7,19 @@
 // SHARE the tiles of B: per k each block loads its own rows of A (8 KiB) and HALF of the columns of B the k needs,
 // and one tcgen05.mma.cta_group::2 (M = 256) reads A from each block's own shared memory and B from both.
 //
-// The skip lists stay what the list builder wrote (one list of steps per 128 x 256 macro tile, gated_multiply.cu).
-// The producers of both blocks walk the upper and the lower macro tile's lists together, k by k (both lists ascend
-// in k), and form for every k the row set of every tile column: 4 bits from the upper list, 4 from the lower.  A
-// maximal range of adjacent columns with the same non-empty row set is a RUN: one instruction (two, for the two
-// K = 16 halves of a tile) with N = 32 * length, whose disable-output-lane mask (8 words: 4 per block) leaves out
-// the tile rows that are not in the set -- so no product outside the lists is ever added.  A run's columns are split
-// between the blocks the way the instruction reads them: the first half of its bytes goes to block 0, the second to
-// block 1, both at the same offset of their stage slot (1 KiB per column tile of the range), one bulk copy each.
+// The skip lists stay what the list builder wrote (one list of steps per 128 x 256 macro tile, gated_multiply.cu);
+// for this kernel a second small kernel (pair_runs_kernel) writes, per pair of macro tiles and per k that has any
+// surviving product in it, one 16-byte RECORD: k and up to 8 RUNS.  It evaluates the same rounded float products
+// against the same threshold as the list builder (one k per lane, 8 x 8 products), so both describe the same set.
+// For one k the record holds the row set of every tile column (4 bits for the upper macro tile's rows, 4 for the
+// lower's); a maximal range of adjacent columns with the same non-empty row set is a run: one instruction (two, for
+// the two K = 16 halves of a tile) with N = 32 * length, whose disable-output-lane mask (8 words: 4 per block) leaves
+// out the tile rows that are not in the set -- so no product outside the lists is ever added.  A run's columns are
+// split between the blocks the way the instruction reads them: the first half of its bytes goes to block 0, the
+// second to block 1, both at the same offset of their stage slot (1 KiB per column tile of the range), one bulk copy
+// each.
 //
-// Roles per block: warp 0 producer (all lanes follow the lists, lane 0 issues copies), warp 1 the MMA issuer in the
+// Roles per block: warp 0 producer (reads the records 32 at a time, lane 0 issues copies), warp 1 the MMA issuer in the
 // leader block and a relay in the other (its block's copies have landed -> arrives on the leader's barrier), warps
 // 2-5 epilogue (tensor memory -> shared-memory turn -> whole rows of C; clears the accumulator behind itself, since
 // every instruction accumulates).  Two accumulators alternate.  Units (pairs of macro tiles) are dealt out round-robin
@@ -32,7 +35,7 @@ constexpr int G_STAGE_BYTES = G_SPS * G_SLOT_BYTES;             // 32 KiB
 constexpr int G_STAGES = 6;                                     // 192 KiB
 constexpr int G_RUNS = 8;                                       // most runs of one k (8 tile columns)
 constexpr int G_THREADS = 192;
-constexpr int G_CTRL_BYTES = 768;
+constexpr int G_CTRL_BYTES = 512;
 constexpr int G_SMEM_BYTES = G_STAGES * G_STAGE_BYTES + G_CTRL_BYTES + 4 * EPI_WARP_BYTES + 128;
 constexpr uint32_t G_TMEM_COLS = 512;
 constexpr uint32_t G_ACC_COLS = MT_C * TILE;                    // 256
@@ -43,15 +46,33 @@ struct GCtrl {
     unsigned long long tmem_full[2];          // accumulator complete (multicast commit)
     unsigned long long tmem_empty[2];         // (leader only) both blocks have drained the accumulator
     unsigned long long drain;
-    uint32_t run_word[G_STAGES][G_SPS][G_RUNS];   // per stage slot: the runs of one k, zero terminated
+    uint4 rec[G_STAGES][G_SPS];               // per stage slot: the record of one k (x == 0xffffffff: slot not used)
     uint32_t stage_last[G_STAGES];            // this stage ends its unit
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 static_assert(sizeof(GCtrl) <= G_CTRL_BYTES, "control block too large");
 
-// run word: bits 0-7 row set (4 upper + 4 lower tile rows), bits 8-11 first tile column, bits 12-15 length
-__device__ __forceinline__ uint32_t run_pack(uint32_t rows8, uint32_t c, uint32_t len) { return rows8 | (c << 8) | (len << 12); }
+// Record of one k of one pair of macro tiles, 128 bits: bits 0-15 k, then 8 runs of 14 bits each
+// (bits 0-7 row set: 4 upper + 4 lower tile rows; bits 8-10 first tile column; bits 11-13 length - 1); a run with an
+// empty row set ends the record.
+__device__ __forceinline__ uint32_t rec_run(const uint4 &r, int i)
+{
+    const int o = 16 + 14 * i, wi = o >> 5, sh = o & 31;
+    const uint32_t lo = wi == 0 ? r.x : wi == 1 ? r.y : wi == 2 ? r.z : r.w;
+    const uint32_t hi = wi == 0 ? r.y : wi == 1 ? r.z : wi == 2 ? r.w : 0u;
+    return __funnelshift_r(lo, hi, sh) & 0x3fffu;
+}
+__device__ __forceinline__ void rec_set_run(uint4 &r, int i, uint32_t run)
+{
+    const int o = 16 + 14 * i, wi = o >> 5, sh = o & 31;
+    const uint64_t v = (uint64_t)run << sh;
+    const uint32_t lo = (uint32_t)v, hi = (uint32_t)(v >> 32);
+    if (wi == 0) { r.x |= lo; r.y |= hi; }
+    else if (wi == 1) { r.y |= lo; r.z |= hi; }
+    else if (wi == 2) { r.z |= lo; r.w |= hi; }
+    else { r.w |= lo; }
+}
 
 __device__ __forceinline__ uint32_t g_cluster_ctarank()
 {
@@ -121,43 +142,97 @@ __device__ __forceinline__ void g_umma_commit(uint32_t bar)
 
 enum { GERR_EMPTY = 21, GERR_FULL = 22, GERR_TMEM_EMPTY = 24, GERR_TMEM_FULL = 25 };
 
-// A reader of one macro tile's step list for a whole warp: 64 consecutive steps are kept in two registers per lane
-// (lane i holds steps base+i and base+32+i); the next 32 are fetched while the current ones are used.
-struct StepWindow {
-    const uint32_t *list;
-    int cnt, pos, base;
-    uint32_t w0, w1;
-    __device__ __forceinline__ void open(const uint32_t *l, int n, int lane)
-    {
-        list = l;
-        cnt = n;
-        pos = 0;
-        base = 0;
-        w0 = lane < n ? __ldg(l + lane) : 0u;
-        w1 = 32 + lane < n ? __ldg(l + 32 + lane) : 0u;
-    }
-    // step number i (pos <= i < pos + 32), the same value in every lane
-    __device__ __forceinline__ uint32_t at(int i) const
-    {
-        const int o = i - base;
-        const uint32_t a = __shfl_sync(0xffffffffu, w0, o & 31), b = __shfl_sync(0xffffffffu, w1, o & 31);
-        return o < 32 ? a : b;
-    }
-    __device__ __forceinline__ void advance(int n, int lane)
-    {
-        pos += n;
-        if (pos - base >= 32) {          // the first register is used up: shift and fetch the next 32 steps
-            base += 32;
-            w0 = w1;
-            w1 = base + 32 + lane < cnt ? __ldg(list + base + 32 + lane) : 0u;
+// Records for the two-SM kernel: one warp per pair of macro tiles, one k per lane.  amax / bmax are the chunk maxima
+// the list builder's first kernel left (largest norm per 4 tile rows of A / 8 tile columns of B and 32 k): a chunk
+// whose largest product is below the threshold holds no survivor and is not read (rounded float multiplication is
+// monotone in each factor).
+__global__ void __launch_bounds__(128)
+pair_runs_kernel(const float *__restrict__ norm_a, const float *__restrict__ norm_b, int row_tiles, int k_tiles,
+                 int n_tiles, float tau, const float *__restrict__ amax, const float *__restrict__ bmax,
+                 uint4 *__restrict__ recs, int32_t *__restrict__ rec_counts)
+{
+    const int lane = threadIdx.x & 31;
+    const int mi_n = (row_tiles + MT_R - 1) / MT_R;
+    const int mj_n = (n_tiles + MT_C - 1) / MT_C;
+    const int kc_n = (k_tiles + 31) / 32;
+    const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (unit >= (mi_n >> 1) * mj_n) return;
+    const int pr = unit / mj_n, mj = unit % mj_n;
+    uint4 *out = recs + (int64_t)unit * k_tiles;
+    int n_out = 0;
+    const bool b_vec = ((n_tiles & 3) == 0) && (mj * MT_C + MT_C <= n_tiles) &&
+                       ((reinterpret_cast<uintptr_t>(norm_b) & 15) == 0);
+    for (int g0 = 0; g0 < kc_n; g0 += 32) {
+        bool alive = false;
+        if (g0 + lane < kc_n) {
+            const float bm = bmax[(int64_t)(g0 + lane) * mj_n + mj];
+            const float p0 = __fmul_rn(amax[(int64_t)(2 * pr) * kc_n + g0 + lane], bm);
+            const float p1 = __fmul_rn(amax[(int64_t)(2 * pr + 1) * kc_n + g0 + lane], bm);
+            alive = !(p0 < tau) || !(p1 < tau);
+        }
+        uint32_t chunks = __ballot_sync(0xffffffffu, alive);
+        while (chunks) {
+            const int kb = (g0 + __ffs(chunks) - 1) * 32;
+            chunks &= chunks - 1;
+            const int k = kb + lane;
+            uint4 rec = make_uint4(0u, 0u, 0u, 0u);
+            bool any = false;
+            if (k < k_tiles) {
+                float a[2 * MT_R], b[MT_C];
+#pragma unroll
+                for (int r = 0; r < 2 * MT_R; r++) {
+                    const int row = pr * 2 * MT_R + r;
+                    a[r] = (row < row_tiles) ? __ldg(norm_a + (int64_t)row * k_tiles + k) : 0.0f;
+                }
+                const float *brow = norm_b + (int64_t)k * n_tiles + mj * MT_C;
+                if (b_vec) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4 *>(brow));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4 *>(brow) + 1);
+                    b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w;
+                    b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+                } else {
+#pragma unroll
+                    for (int cc = 0; cc < MT_C; cc++) b[cc] = (mj * MT_C + cc < n_tiles) ? __ldg(brow + cc) : 0.0f;
+                }
+                // row set of every column, then the runs: adjacent columns with the same non-empty set
+                uint32_t prev = 0, c0 = 0, len = 0;
+                int n_runs = 0;
+#pragma unroll
+                for (int cc = 0; cc <= MT_C; cc++) {
+                    uint32_t rows = 0;
+                    if (cc < MT_C && mj * MT_C + cc < n_tiles) {
+#pragma unroll
+                        for (int r = 0; r < 2 * MT_R; r++) {
+                            const int row = pr * 2 * MT_R + r;
+                            if (row < row_tiles && __fmul_rn(a[r], b[cc]) >= tau) rows |= 1u << r;
+                        }
+                    }
+                    if (rows != prev || cc == MT_C) {
+                        if (prev) {
+                            rec_set_run(rec, n_runs, prev | (c0 << 8) | ((len - 1u) << 11));
+                            n_runs++;
+                        }
+                        prev = rows;
+                        c0 = (uint32_t)cc;
+                        len = 0;
+                    }
+                    len++;
+                }
+                any = n_runs > 0;
+                rec.x |= (uint32_t)k;
+            }
+            const uint32_t have = __ballot_sync(0xffffffffu, any);
+            if (any) out[n_out + __popc(have & ((1u << lane) - 1u))] = rec;
+            n_out += __popc(have);
         }
     }
-    __device__ __forceinline__ bool done() const { return pos >= cnt; }
-};
+    if (lane == 0) rec_counts[unit] = n_out;
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
 gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restrict__ half_b,
-                            const uint32_t *__restrict__ steps, const int32_t *__restrict__ step_counts,
+                            const int32_t *__restrict__ step_counts,
+                            const uint4 *__restrict__ recs, const int32_t *__restrict__ rec_counts,
                             spamm_list_scalars *__restrict__ sc, int row_tiles, int k_tiles, int n_tiles,
                             float *__restrict__ c, int64_t ldc, int mode)
 {
@@ -166,7 +241,6 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
     const float acc_scale = (mode & GM_LOW_OPERAND) ? 1.0f / SPLIT_LOW_SCALE : 1.0f;
     const int mi_n = (row_tiles + MT_R - 1) / MT_R;
     const int mj_n = (n_tiles + MT_C - 1) / MT_C;
-    const int64_t cap = (int64_t)STEP_CAP_PER_K * k_tiles;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -226,131 +300,92 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
         *mj = in_band / rows_here;
         *pr = band * band_rows + in_band % rows_here;
     };
-    // steps of the unit's upper and lower macro tile
-    auto unit_counts = [&](int pr, int mj, int *cu, int *cl) {
-        *cu = step_count_of(step_counts[(2 * pr) * mj_n + mj]);
-        *cl = step_count_of(step_counts[(2 * pr + 1) * mj_n + mj]);
-    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
-        // Every lane follows the two lists (the values are the same in all lanes); lane 0 issues the copies.
+        // The warp reads the unit's records 32 at a time (one per lane, the next 32 fetched meanwhile); every lane
+        // follows them (the values are the same in all lanes), lane 0 issues the copies.
         uint32_t slot = 0;
         bool ok = true;
         for (int u = cluster_id; u < n_units && ok; u += n_clusters) {
-            int pr, mj, cu, cl;
+            int pr, mj;
             unit_at(u, &pr, &mj);
-            unit_counts(pr, mj, &cu, &cl);
-            if (cu + cl == 0) continue;
+            const int unit = pr * mj_n + mj;
+            const int cnt = rec_counts[unit];
+            if (cnt == 0) continue;
+            const uint4 *list = recs + (int64_t)unit * k_tiles;
             const int mi = 2 * pr + (int)rank;
             const uint8_t *a_base = half_a + (int64_t)mi * k_tiles * A_SLAB_BYTES;
             const uint8_t *b_base = half_b + (int64_t)mj * B_SLAB_BYTES;
-            StepWindow up, lo;
-            up.open(steps + (int64_t)((2 * pr) * mj_n + mj) * cap, cu, lane);
-            lo.open(steps + (int64_t)((2 * pr + 1) * mj_n + mj) * cap, cl, lane);
-            int n_slots = 0;
-            uint32_t bytes = 0;
-            uint32_t s = slot % G_STAGES;
-            bool stage_open = false;
-            while ((!up.done() || !lo.done()) && ok) {
-                // the next k: the smaller of the two lists' current k
-                const uint32_t ku = up.done() ? 0xffffffffu : step_k(up.at(up.pos));
-                const uint32_t kl = lo.done() ? 0xffffffffu : step_k(lo.at(lo.pos));
-                const uint32_t k = min(ku, kl);
-                // row set of every tile column, 8 bits per column in one word: 4 bits from the upper list (low), 4 from
-                // the lower
-                uint64_t R = 0;
-                if (ku == k) {
-                    int n = 0;
+            const uint4 none = make_uint4(0u, 0u, 0u, 0u);
+            uint4 next = lane < cnt ? __ldg(list + lane) : none;
+            for (int i0 = 0; i0 < cnt && ok; i0 += 32) {
+                const uint4 mine = next;
+                next = i0 + 32 + lane < cnt ? __ldg(list + i0 + 32 + lane) : none;
+                const int nb = min(32, cnt - i0);
+                for (int j = 0; j < nb && ok; j++) {
+                    uint4 rec;
+                    rec.x = __shfl_sync(0xffffffffu, mine.x, j);
+                    rec.y = __shfl_sync(0xffffffffu, mine.y, j);
+                    rec.z = __shfl_sync(0xffffffffu, mine.z, j);
+                    rec.w = __shfl_sync(0xffffffffu, mine.w, j);
+                    const int t = (i0 + j) % G_SPS;                 // slot inside the stage
+                    const bool last = i0 + j == cnt - 1;
+                    const uint32_t s = slot % G_STAGES;
+                    if (lane == 0) {
+                        if (t == 0) {
+                            // a new stage: wait until the multiplies that read its previous contents are done
+                            ok = wait_bounded(smem_u32(&ctrl->empty[s]), ((slot / G_STAGES) & 1u) ^ 1u, abort_flag, err,
+                                              GERR_EMPTY);
+                        }
+                        if (ok) {
+                            const uint32_t bar = smem_u32(&ctrl->full[s]);
+                            const uint32_t a_slot = smem_u32(smem + s * G_STAGE_BYTES) + t * A_SLAB_BYTES;
+                            const uint32_t b_slot = smem_u32(smem + s * G_STAGE_BYTES) + G_SPS * A_SLAB_BYTES +
+                                                    t * (B_SLAB_BYTES / 2);
+                            const uint32_t k = rec.x & 0xffffu;
+                            const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
+                            uint32_t bytes = 0, rows_any = 0;
 #pragma unroll 1
-                    for (; n < STEP_CAP_PER_K && up.pos + n < up.cnt; n++) {
-                        const uint32_t w = up.at(up.pos + n);
-                        if (step_k(w) != k) break;
-#pragma unroll
-                        for (int cc = 0; cc < MT_C; cc++)
-                            if ((step_cols(w) >> cc) & 1u) R |= (uint64_t)step_rows(w) << (8 * cc);
+                            for (int r = 0; r < G_RUNS; r++) {
+                                const uint32_t run = rec_run(rec, r);
+                                if ((run & 0xffu) == 0u) break;
+                                const uint32_t c0 = (run >> 8) & 7u, len = ((run >> 11) & 7u) + 1u;
+                                rows_any |= run & 0xffu;
+                                // the run's 2 KiB tiles are adjacent in B's slab: the first half of the bytes to block 0,
+                                // the second to block 1, both at 1 KiB per tile of the range from the slot's start
+                                bulk_g2s(b_slot + c0 * (TILE_BYTES / 2), b_src + c0 * TILE_BYTES + rank * len * (TILE_BYTES / 2),
+                                         len * (TILE_BYTES / 2), bar);
+                                bytes += len * (TILE_BYTES / 2);
+                            }
+                            // the rows of A this block owns: one tile when a single row takes part, else the slab
+                            const uint32_t own = (rows_any >> (4 * rank)) & 0xfu;
+                            if (own) {
+                                const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
+                                if (__popc(own) == 1) {
+                                    const uint32_t q = (uint32_t)(__ffs(own) - 1);
+                                    bulk_g2s(a_slot + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
+                                    bytes += TILE_BYTES;
+                                } else {
+                                    bulk_g2s(a_slot, a_src, A_SLAB_BYTES, bar);
+                                    bytes += A_SLAB_BYTES;
+                                }
+                            }
+                            ctrl->rec[s][t] = rec;
+                            // a copy may complete before the bytes it brings are announced: the barrier's count of
+                            // pending bytes is signed, and its phase cannot end before the arrival below
+                            if (t == G_SPS - 1 || last) {
+                                if (t < G_SPS - 1) ctrl->rec[s][t + 1].x = 0xffffffffu;
+                                ctrl->stage_last[s] = last ? 1u : 0u;
+                                mbar_arrive_expect_tx(bar, bytes);
+                            } else {
+                                asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes)
+                                             : "memory");
+                            }
+                        }
                     }
-                    up.advance(n, lane);
-                }
-                if (kl == k) {
-                    int n = 0;
-#pragma unroll 1
-                    for (; n < STEP_CAP_PER_K && lo.pos + n < lo.cnt; n++) {
-                        const uint32_t w = lo.at(lo.pos + n);
-                        if (step_k(w) != k) break;
-#pragma unroll
-                        for (int cc = 0; cc < MT_C; cc++)
-                            if ((step_cols(w) >> cc) & 1u) R |= (uint64_t)step_rows(w) << (8 * cc + 4);
-                    }
-                    lo.advance(n, lane);
-                }
-                if (!stage_open) {
-                    // a new stage: wait until the multiplies that read its previous contents are done
-                    s = slot % G_STAGES;
-                    const uint32_t ph = (slot / G_STAGES) & 1u;
-                    if (lane == 0) ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, GERR_EMPTY);
                     ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) break;
-                    stage_open = true;
-                    n_slots = 0;
-                    bytes = 0;
-                }
-                // this k's slot: rows of A this block owns, runs of B
-                const uint32_t a_slot = smem_u32(smem + s * G_STAGE_BYTES) + n_slots * A_SLAB_BYTES;
-                const uint32_t b_slot = smem_u32(smem + s * G_STAGE_BYTES) + G_SPS * A_SLAB_BYTES + n_slots * (B_SLAB_BYTES / 2);
-                const uint32_t bar = smem_u32(&ctrl->full[s]);
-                // tile rows of this block that take part in some column
-                uint64_t fold = R >> (4 * rank);
-                fold |= fold >> 32;
-                fold |= fold >> 16;
-                fold |= fold >> 8;
-                const uint32_t own = (uint32_t)fold & 0xfu;
-                const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
-                const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
-                if (lane == 0 && own) {
-                    if (__popc(own) == 1) {
-                        const uint32_t q = (uint32_t)(__ffs(own) - 1);
-                        bulk_g2s(a_slot + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
-                    } else {
-                        bulk_g2s(a_slot, a_src, A_SLAB_BYTES, bar);
-                    }
-                }
-                if (own) bytes += (__popc(own) == 1) ? TILE_BYTES : A_SLAB_BYTES;
-                int n_runs = 0;
-#pragma unroll 1
-                for (int c0 = 0; c0 < MT_C;) {
-                    const uint32_t r0 = (uint32_t)(R >> (8 * c0)) & 0xffu;
-                    if (r0 == 0) {
-                        c0++;
-                        continue;
-                    }
-                    int len = 1;
-                    while (c0 + len < MT_C && ((uint32_t)(R >> (8 * (c0 + len))) & 0xffu) == r0) len++;
-                    // the run's 2 KiB tiles are adjacent in B's slab: the first half of the bytes to block 0, the second
-                    // to block 1, both at 1 KiB per tile of the range from the slot's start
-                    if (lane == 0) {
-                        bulk_g2s(b_slot + (uint32_t)c0 * (TILE_BYTES / 2),
-                                 b_src + (uint32_t)c0 * TILE_BYTES + rank * (uint32_t)len * (TILE_BYTES / 2),
-                                 (uint32_t)len * (TILE_BYTES / 2), bar);
-                        ctrl->run_word[s][n_slots][n_runs] = run_pack(r0, (uint32_t)c0, (uint32_t)len);
-                    }
-                    bytes += (uint32_t)len * (TILE_BYTES / 2);
-                    n_runs++;
-                    c0 += len;
-                }
-                if (lane == 0 && n_runs < G_RUNS) ctrl->run_word[s][n_slots][n_runs] = 0u;
-                n_slots++;
-                const bool last = up.done() && lo.done();
-                if (n_slots == G_SPS || last) {
-                    if (lane == 0) {
-                        if (n_slots < G_SPS) ctrl->run_word[s][n_slots][0] = 0u;
-                        ctrl->stage_last[s] = last ? 1u : 0u;
-                        // the copies above may already have completed their bytes: the barrier's pending count goes
-                        // negative until this arrival adds the expectation, which is allowed
-                        mbar_arrive_expect_tx(bar, bytes);
-                    }
-                    stage_open = false;
-                    slot++;
+                    if (t == G_SPS - 1 || last) slot++;
                 }
             }
         }
@@ -372,10 +407,9 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
                 const uint64_t desc0 = smem_desc(0);
                 const uint32_t stage0 = smem_u32(smem);
                 for (int u = cluster_id; u < n_units && ok; u += n_clusters) {
-                    int pr, mj, cu, cl;
+                    int pr, mj;
                     unit_at(u, &pr, &mj);
-                    unit_counts(pr, mj, &cu, &cl);
-                    if (cu + cl == 0) continue;
+                    if (rec_counts[pr * mj_n + mj] == 0) continue;
                     const uint32_t buf = acc_iter & 1u;
                     ok = g_wait_cluster(smem_u32(&ctrl->tmem_empty[buf]), ((acc_iter >> 1) & 1u) ^ 1u, abort_flag, err,
                                         GERR_TMEM_EMPTY);
@@ -394,17 +428,16 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
                         if (lane == 0) {
 #pragma unroll 1
                             for (int t = 0; t < G_SPS; t++) {
+                                const uint4 rec = ctrl->rec[s][t];
+                                if (rec.x == 0xffffffffu) break;       // a stage that is not full: no further slots
                                 const uint64_t da = desc0 + (uint64_t)((a_stage + t * A_SLAB_BYTES) >> 4);
                                 const uint32_t b_slot = b_stage + t * (B_SLAB_BYTES / 2);
-                                bool end = false;
 #pragma unroll 1
                                 for (int r = 0; r < G_RUNS; r++) {
-                                    const uint32_t w = ctrl->run_word[s][t][r];
-                                    if (w == 0u) {
-                                        end = r == 0;
-                                        break;
-                                    }
-                                    const uint32_t rows8 = w & 0xffu, c0 = (w >> 8) & 0xfu, len = (w >> 12) & 0xfu;
+                                    const uint32_t run = rec_run(rec, r);
+                                    const uint32_t rows8 = run & 0xffu;
+                                    if (rows8 == 0u) break;
+                                    const uint32_t c0 = (run >> 8) & 7u, len = ((run >> 11) & 7u) + 1u;
                                     uint32_t m[8];
 #pragma unroll
                                     for (int i = 0; i < 8; i++) m[i] = ((rows8 >> i) & 1u) ? 0u : 0xffffffffu;
@@ -415,7 +448,6 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
                                     g_umma_masked(dcol, da, db, idesc, m);
                                     g_umma_masked(dcol, da + 16u, db + 16u, idesc, m);
                                 }
-                                if (end) break;      // a stage that is not full: no further slots
                             }
                             g_umma_commit(smem_u32(&ctrl->empty[s]));
                         }
@@ -434,10 +466,9 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
             } else {
                 // -------------------------------------------------------------- other block: relay "my copies landed"
                 for (int u = cluster_id; u < n_units && ok; u += n_clusters) {
-                    int pr, mj, cu, cl;
+                    int pr, mj;
                     unit_at(u, &pr, &mj);
-                    unit_counts(pr, mj, &cu, &cl);
-                    if (cu + cl == 0) continue;
+                    if (rec_counts[pr * mj_n + mj] == 0) continue;
                     for (bool last = false; !last;) {
                         const uint32_t s = slot % G_STAGES, ph = (slot / G_STAGES) & 1u;
                         ok = wait_bounded(smem_u32(&ctrl->full[s]), ph, abort_flag, err, GERR_FULL);
@@ -459,12 +490,11 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
         unsigned int done = 0;
         bool ok = true;
         for (int u = cluster_id; u < n_units && ok; u += n_clusters) {
-            int pr, mj, cu, cl;
+            int pr, mj;
             unit_at(u, &pr, &mj);
-            unit_counts(pr, mj, &cu, &cl);
             const int mi = 2 * pr + (int)rank;
             done++;
-            if (cu + cl == 0) {
+            if (rec_counts[pr * mj_n + mj] == 0) {
                 // nothing survives in either macro tile: zeros, unless C was cleared beforehand
                 if (!c_zeroed) {
                     // zero_fill (see gated_multiply.cu): 128 threads, 64 columns of float4 each pass
@@ -488,7 +518,7 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
             const bool row_ok = row < rows_total;
             // this block's own macro tile may be one without steps while its partner's has some: with C cleared
             // beforehand (or holding a partial result) it is left alone, but the accumulator is still cleared
-            const bool write = !(c_zeroed && (rank == 0 ? cu : cl) == 0);
+            const bool write = !(c_zeroed && step_count_of(step_counts[mi * mj_n + mj]) == 0);
             float *cblock = c + (int64_t)(row - lane) * ldc + (int64_t)mj * (MT_C * TILE);
 #pragma unroll 1
             for (int cc = 0; cc < MT_C; cc++) {
@@ -519,12 +549,21 @@ gated_multiply_gpair_kernel(const uint8_t *__restrict__ half_a, const uint8_t *_
     }
 }
 
-int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,
-                                const int32_t *d_step_counts, spamm_list_scalars *d_scalars, int row_tiles, int k_tiles,
+size_t gated_multiply_gpair_scratch_bytes(int row_tiles, int k_tiles, int n_tiles)
+{
+    const size_t units = (size_t)(ceil_div(row_tiles, MT_R) / 2) * ceil_div(n_tiles, MT_C);
+    return units * ((size_t)k_tiles * sizeof(uint4) + 16);
+}
+
+int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, const float *d_norm_a, const float *d_norm_b,
+                                float tau, const void *d_chunk_max, const int32_t *d_step_counts, void *d_scratch,
+                                bool build_records, spamm_list_scalars *d_scalars, int row_tiles, int k_tiles,
                                 int n_tiles, float *d_c, int64_t ldc, int mode, cudaStream_t stream)
 {
     const int mi_n = ceil_div(row_tiles, MT_R), mj_n = ceil_div(n_tiles, MT_C);
     if (mi_n < 2 || mj_n == 0 || k_tiles == 0) return SPAMM_OK;
+    if (!d_scratch || !d_norm_a || !d_norm_b || !d_chunk_max || (reinterpret_cast<uintptr_t>(d_scratch) & 15))
+        return SPAMM_ERR_INVALID;
     static int sm_count_of[64] = {};        // per device, written once with the same value by whoever comes first
     int dev = 0;
     SPAMM_CUDA_TRY(cudaGetDevice(&dev));
@@ -537,12 +576,22 @@ int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, cons
         sm_count_of[dev] = sms;
     }
     const int64_t n_units = (int64_t)(mi_n / 2) * mj_n;
+    // scratch: the records of every unit (k_tiles each), then the units' record counts
+    uint4 *recs = static_cast<uint4 *>(d_scratch);
+    int32_t *rec_counts = reinterpret_cast<int32_t *>(recs + n_units * k_tiles);
+    if (build_records) {
+        const int kc_n = ceil_div(k_tiles, 32);
+        const float *amax = static_cast<const float *>(d_chunk_max);
+        const float *bmax = amax + (size_t)mi_n * kc_n;
+        pair_runs_kernel<<<(unsigned)((n_units + 3) / 4), 128, 0, stream>>>(d_norm_a, d_norm_b, row_tiles, k_tiles, n_tiles,
+                                                                           tau, amax, bmax, recs, rec_counts);
+    }
     int clusters = sm_count_of[dev] / 2;
     if (clusters > n_units) clusters = (int)n_units;
     if (clusters < 1) return SPAMM_OK;
     gated_multiply_gpair_kernel<<<2 * clusters, G_THREADS, G_SMEM_BYTES, stream>>>(
-        static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_steps, d_step_counts, d_scalars,
-        row_tiles, k_tiles, n_tiles, d_c, ldc, mode);
+        static_cast<const uint8_t *>(d_half_a), static_cast<const uint8_t *>(d_half_b), d_step_counts, recs, rec_counts,
+        d_scalars, row_tiles, k_tiles, n_tiles, d_c, ldc, mode);
     SPAMM_CUDA_TRY(cudaGetLastError());
     return SPAMM_OK;
 }

@@ -157,9 +157,39 @@ static int pairs_choice(const spamm_plan *p)
 {
     if (p->multiply_mode == SPAMM_MULTIPLY_ONE_SM) return GM_PAIRS_NONE;
     if (p->multiply_mode == SPAMM_MULTIPLY_GATED_PAIRS) return GM_PAIRS_GATED;
-    if (p->dense_hint == 1) return GM_PAIRS_DENSE;
-    if (p->gpair_hint == 1) return GM_PAIRS_GATED;
+    // The gated kernel on pairs of SMs is never chosen automatically: measured on long half-full lists (a lattice
+    // density matrix, N = 32768) it moves a third fewer bytes but keeps fewer of them in flight (its ring slots are
+    // sized for the largest k, and a stage passes through both blocks before it is free again), 48 ms against 37.5 ms.
     return p->dense_hint != 0 ? GM_PAIRS_DENSE : GM_PAIRS_NONE;      // unknown yet: the dense kernel checks by itself
+}
+
+// The gated two-SM kernel's records live in a buffer of their own (16 bytes per k and pair of macro tiles), allocated
+// the first time that kernel is chosen.  Fills `args` for a multiply over tile rows [t0, t0+tiles) of the plan's block
+// (t0 a multiple of 8); returns GM_PAIRS_NONE in *pairs when the buffer cannot be had, so that the caller falls back.
+static void gpair_args_for(spamm_plan *p, int t0, const float *norm_a, GpairArgs *args, int *pairs)
+{
+    if (*pairs != GM_PAIRS_GATED) return;
+    if (!p->d_gpair) {
+        const size_t bytes = gated_multiply_gpair_scratch_bytes(p->row_tiles, p->k_tiles, p->n_tiles) + 16 * MAX_CHUNKS;
+        if (t0 % (2 * MT_R) || cudaMalloc(&p->d_gpair, bytes ? bytes : 16) != cudaSuccess) {
+            cudaGetLastError();
+            p->d_gpair = nullptr;
+            *pairs = GM_PAIRS_NONE;
+            return;
+        }
+    }
+    if (t0 % (2 * MT_R)) {
+        *pairs = GM_PAIRS_NONE;
+        return;
+    }
+    // every pair of macro-tile rows before t0 has its records and counts before this block's
+    const size_t units_before = (size_t)(t0 / (2 * MT_R)) * p->mj_n;
+    args->norm_a = norm_a;
+    args->norm_b = p->d_norm_b;
+    args->tau = p->last_tau;
+    args->chunk_max = p->d_list_scratch;
+    args->scratch = static_cast<char *>(p->d_gpair) + units_before * ((size_t)p->k_tiles * 16 + 16);
+    args->build = true;
 }
 
 // (Re)builds the macro-tile orders for the chunk shapes of the pipelined spamm_multiply.
@@ -298,8 +328,8 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
         if (target < CHUNK_MIN_BYTES) target = CHUNK_MIN_BYTES;
         if (target > CHUNK_TARGET_BYTES) target = CHUNK_TARGET_BYTES;
         int ct = (int)((target + row_bytes - 1) / row_bytes);
-        ct = (ct + MT_R - 1) / MT_R * MT_R;
-        while (p->row_tiles > 0 && ceil_div(p->row_tiles, ct) > MAX_CHUNKS) ct += MT_R;
+        ct = (ct + 2 * MT_R - 1) / (2 * MT_R) * (2 * MT_R);      // whole pairs of macro-tile rows
+        while (p->row_tiles > 0 && ceil_div(p->row_tiles, ct) > MAX_CHUNKS) ct += 2 * MT_R;
         p->chunk_tiles = ct;
         p->n_chunks = p->row_tiles > 0 ? ceil_div(p->row_tiles, ct) : 1;
     }
@@ -378,7 +408,7 @@ int spamm_plan_destroy(spamm_plan *p)
     if (p->h_peer_error) cudaFreeHost(p->h_peer_error);
     cudaFree(p->d_counts); cudaFree(p->d_step_counts); cudaFree(p->d_steps);
     cudaFree(p->d_half_a); cudaFree(p->d_half_b); cudaFree(p->d_cleared); cudaFree(p->d_order);
-    cudaFree(p->d_low_a); cudaFree(p->d_low_b);
+    cudaFree(p->d_low_a); cudaFree(p->d_low_b); cudaFree(p->d_gpair);
     cudaFree(p->d_busy); cudaFree(p->d_tile_list); cudaFree(p->d_list_scratch);
     cudaFree(p->d_cv_scratch); cudaFree(p->d_cv_count); cudaFree(p->d_err_scratch);
     if (p->h_scalars) cudaFreeHost(p->h_scalars);
@@ -625,6 +655,8 @@ static int build_lists_impl(spamm_plan *p, float tau, bool whole_step)
     if (!p->have_norms) return SPAMM_ERR_STATE;
     DeviceGuard guard(p->device);
     p->active_scalars = 1;
+    p->last_tau = tau;
+    p->gpair_valid = false;
     PeerWait wait{p->d_peer_flags, p->peer_world, p->peer_epoch, p->d_peer_error, PEER_WAIT_LIMIT_NS};
     if (whole_step) {
         int st = spamm_clear_c_early(p);
@@ -676,9 +708,15 @@ int spamm_gated_multiply(spamm_plan *p)
         const bool zeroed = p->c_zero_pending;
         if (zeroed) SPAMM_CUDA_TRY(cudaStreamWaitEvent(p->stream, p->ev_zero[1], 0));
         p->c_zero_pending = false;      // consumed: a second multiply on the same lists writes all of C itself
+        int pairs = pairs_choice(p);
+        GpairArgs gp{};
+        gpair_args_for(p, 0, p->d_norm_a, &gp, &pairs);
+        gp.build = !p->gpair_valid;
         int st = gated_multiply_launch(p->d_half_a, p->d_half_b, p->d_steps, p->d_step_counts, p->d_order, p->d_busy,
                                        p->scalars(), p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N,
-                                       !p->queues_clean, pairs_choice(p), zeroed ? GM_C_ZEROED : 0, p->stream);
+                                       !p->queues_clean, pairs, zeroed ? GM_C_ZEROED : 0, p->stream, &gp);
+        if (pairs == GM_PAIRS_GATED) p->gpair_valid = true;
+        gp.build = false;
         p->queues_clean = false;
         if (st) return st;
         p->launches++;
@@ -689,8 +727,8 @@ int spamm_gated_multiply(spamm_plan *p)
                 st = gated_multiply_launch(pass == 0 ? p->d_half_a : p->d_low_a, pass == 0 ? p->d_low_b : p->d_half_b,
                                            p->d_steps, p->d_step_counts, p->d_order, p->d_busy, p->scalars(),
                                            p->row_tiles, p->k_tiles, p->n_tiles, p->d_c, p->N, true,
-                                           pairs_choice(p) == GM_PAIRS_GATED ? GM_PAIRS_GATED : GM_PAIRS_NONE,
-                                           GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, p->stream);
+                                           pairs == GM_PAIRS_GATED ? GM_PAIRS_GATED : GM_PAIRS_NONE,
+                                           GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, p->stream, &gp);
                 if (st) return st;
                 p->launches++;
             }
@@ -833,17 +871,23 @@ static int run_chunk(spamm_plan *p, int chunk, int t0, int tiles, float tau, con
     if ((st = pack_half_launch(a, p->d_b, tiles, p->k_tiles, p->n_tiles, p->d_tile_list, sc, half_a, p->d_half_b, low_a,
                                split ? p->d_low_b : nullptr, true, stream)))
         return st;
+    int pairs = pairs_choice(p);
+    GpairArgs gp{};
+    p->last_tau = tau;
+    gpair_args_for(p, t0, norm_a, &gp, &pairs);
     if ((st = gated_multiply_launch(half_a, p->d_half_b, p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0,
                                     d_order, p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
-                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, pairs_choice(p), 0, stream)))
+                                    p->d_c + (size_t)t0 * TILE * p->N, p->N, false, pairs, 0, stream, &gp)))
         return st;
+    gp.build = false;
+    p->gpair_valid = false;         // these records are a chunk's, not the whole block's
     for (int pass = 0; split && pass < 2; pass++) {
         if ((st = gated_multiply_launch(pass == 0 ? half_a : low_a, pass == 0 ? p->d_low_b : p->d_half_b,
                                         p->d_steps + mt0 * p->step_cap(), p->d_step_counts + mt0, d_order,
                                         p->d_busy + mt0, sc, tiles, p->k_tiles, p->n_tiles,
                                         p->d_c + (size_t)t0 * TILE * p->N, p->N, true,
-                                        pairs_choice(p) == GM_PAIRS_GATED ? GM_PAIRS_GATED : GM_PAIRS_NONE,
-                                        GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, stream)))
+                                        pairs == GM_PAIRS_GATED ? GM_PAIRS_GATED : GM_PAIRS_NONE,
+                                        GM_C_ZEROED | GM_ACCUMULATE | GM_LOW_OPERAND, stream, &gp)))
             return st;
         p->launches++;
     }

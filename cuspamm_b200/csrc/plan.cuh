@@ -71,6 +71,9 @@ struct spamm_plan {
 
     int active_scalars = 1;             // how many sets of counters the last operation used (one per chunk)
     bool queues_clean = false;          // the multiply's two work counters are zero (cleared by the list build or the packing kernel)
+    void *d_gpair = nullptr;            // records of the gated two-SM multiply kernel, allocated when it is first chosen
+    bool gpair_valid = false;           // they belong to the current lists
+    float last_tau = 0.0f;              // threshold of the current lists
     int multiply_mode = 0;              // SPAMM_MULTIPLY_*: which multiply kernels may run, see spamm_plan_set_multiply_mode
     int gpair_hint = -1;                // last counters read: long lists in most macro tiles (-1: unknown)
     int dense_hint = -1;                // last counters read: were at least half of the macro tiles dense (-1: unknown)

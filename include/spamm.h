@@ -262,12 +262,12 @@ int spamm_plan_set_pack_mode(spamm_plan *plan, int mode);
  * Which multiply kernels spamm_gated_multiply may use.  Results are the same in every mode (up to the order of the float
  * additions inside the tensor cores).
  *   SPAMM_MULTIPLY_AUTO         (default) by the counters of the plan's previous step: mostly dense macro tiles go to
- *                               pairs of SMs ungated; long lists in most macro tiles go to the gated kernel on pairs of
- *                               SMs (two vertically adjacent macro tiles share the tiles of B they load: a third less
- *                               traffic from L2 into the SMs, which is what bounds such workloads); everything else to
- *                               the one-SM kernel;
+ *                               pairs of SMs ungated (four macro tiles per pair), everything else to the one-SM kernel;
  *   SPAMM_MULTIPLY_ONE_SM       the one-SM kernel only;
- *   SPAMM_MULTIPLY_GATED_PAIRS  the gated kernel on pairs of SMs for every pair of macro-tile rows.
+ *   SPAMM_MULTIPLY_GATED_PAIRS  the gated kernel on pairs of SMs for every pair of macro-tile rows: two vertically
+ *                               adjacent macro tiles share the tiles of B they load, a third less traffic from L2
+ *                               into the SMs.  Allocates 16 bytes per k and pair of macro tiles at first use.  Not
+ *                               chosen automatically: as measured it is slower than the one-SM kernel.
  */
 enum { SPAMM_MULTIPLY_AUTO = 0, SPAMM_MULTIPLY_ONE_SM = 1, SPAMM_MULTIPLY_GATED_PAIRS = 2 };
 int spamm_plan_set_multiply_mode(spamm_plan *plan, int mode);
