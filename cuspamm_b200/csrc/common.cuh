@@ -52,6 +52,12 @@ int peer_wait_selftest_launch(const PeerWait &w, cudaStream_t stream);
 // and raises this GPU's arrival flag, value `epoch`, on every GPU.
 int push_share_launch(const float *d_local_share, int64_t share, int64_t map_offset, const PeerTargets &t, int rank,
                       unsigned int epoch, cudaStream_t stream);
+// The norm maps of this GPU's rows of A and of its share of B's tile rows in one launch whose last block of the share
+// also stores the share into every other GPU's map and raises the arrival flags (d_counter: one word, zero on entry).
+int norm_map_pair_push_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a, const float *d_xb,
+                              int rows_b, int cols_b, int64_t ldb, float *d_local_share, int64_t map_offset,
+                              const PeerTargets &t, int rank, unsigned int epoch, unsigned int *d_counter,
+                              cudaStream_t stream);
 // Both norm maps AND the half conversion of every tile of A and B in one launch (for mostly surviving workloads).
 int norm_pack_pair_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a, void *d_half_a,
                           const float *d_xb, int rows_b, int cols_b, int64_t ldb, float *d_map_b, void *d_half_b,

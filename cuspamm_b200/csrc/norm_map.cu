@@ -231,6 +231,71 @@ push_share_kernel(const float4 *__restrict__ src, int64_t vecs, int64_t map_offs
     }
 }
 
+// The norm maps of a GPU's rows of A and of its share of B's tile rows in ONE launch that also delivers the share: the
+// blocks of the share come first in the grid; each of them, when its values are written, counts itself in, and the one
+// that finds itself last copies the whole share into every other GPU's map (peer stores) and raises the flags.  The
+// rest of the grid is still reading A meanwhile, so the exchange costs neither a launch nor time on the stream.
+__global__ void __launch_bounds__(256)
+norm_map_pair_push_kernel(const float *__restrict__ xb, int tile_rows_b, int tile_cols_b, int64_t ldb,
+                          float *__restrict__ share, unsigned int blocks_b, const float *__restrict__ xa,
+                          int tile_rows_a, int tile_cols_a, int64_t lda, float *__restrict__ map_a, int64_t share_vecs,
+                          int64_t map_offset_vecs, PeerTargets t, int self, unsigned int epoch,
+                          unsigned int *__restrict__ counter)
+{
+    if (blockIdx.x >= blocks_b) {
+        norm_strip(xa, tile_rows_a, tile_cols_a, lda, map_a, (int64_t)(blockIdx.x - blocks_b) * 8 + (threadIdx.x >> 5));
+        return;
+    }
+    norm_strip(xb, tile_rows_b, tile_cols_b, ldb, share, (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5));
+    __shared__ unsigned int ticket;
+    __syncthreads();                                // every warp of the block has written its norms
+    if (threadIdx.x == 0) {
+        __threadfence();                            // ... and they are visible before the block counts itself in
+        ticket = atomicAdd(counter, 1u);
+    }
+    __syncthreads();
+    if (ticket != blocks_b - 1) return;
+    __threadfence();                                // the last block: everybody else's norms are visible to it
+    const float4 *src = reinterpret_cast<const float4 *>(share);
+    for (int d = 0; d < t.n; d++) {
+        if (d == self) continue;
+        float4 *dst = reinterpret_cast<float4 *>(t.map[d]) + map_offset_vecs;
+        for (int64_t i = threadIdx.x; i < share_vecs; i += blockDim.x) dst[i] = __ldcg(src + i);
+    }
+    __syncthreads();                                // orders the block's stores before the fence below
+    if (threadIdx.x == 0) {
+        *counter = 0u;                              // for the next step (stream order)
+        __threadfence_system();
+        for (int d = 0; d < t.n; d++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(t.flags[d] + self), "r"(epoch) : "memory");
+    }
+}
+
+int norm_map_pair_push_launch(const float *d_xa, int rows_a, int cols_a, int64_t lda, float *d_map_a, const float *d_xb,
+                              int rows_b, int cols_b, int64_t ldb, float *d_local_share, int64_t map_offset,
+                              const PeerTargets &t, int rank, unsigned int epoch, unsigned int *d_counter,
+                              cudaStream_t stream)
+{
+    if (!d_xa || !d_map_a || !d_xb || !d_local_share || !d_counter || rows_a < 0 || cols_a <= 0 || rows_b <= 0 ||
+        cols_b <= 0 || rows_a % TILE || cols_a % TILE || rows_b % TILE || cols_b % TILE || lda < cols_a || ldb < cols_b ||
+        (lda & 3) || (ldb & 3) || (reinterpret_cast<uintptr_t>(d_xa) & 15) || (reinterpret_cast<uintptr_t>(d_xb) & 15) ||
+        t.n <= 0 || t.n > MAX_PEERS || rank < 0 || rank >= t.n)
+        return SPAMM_ERR_INVALID;
+    const int tra = rows_a / TILE, tca = cols_a / TILE, trb = rows_b / TILE, tcb = cols_b / TILE;
+    const int64_t share = (int64_t)trb * tcb;
+    if ((share & 3) || (map_offset & 3) || (reinterpret_cast<uintptr_t>(d_local_share) & 15) ||
+        d_local_share != t.map[rank] + map_offset)
+        return SPAMM_ERR_UNSUPPORTED;
+    const int64_t blocks_a = ((int64_t)tra * ((tca + 3) / 4) + 7) / 8;
+    const int64_t blocks_b = ((int64_t)trb * ((tcb + 3) / 4) + 7) / 8;
+    if (blocks_a + blocks_b > 0x7fffffffLL) return SPAMM_ERR_UNSUPPORTED;
+    norm_map_pair_push_kernel<<<(unsigned)(blocks_a + blocks_b), 256, 0, stream>>>(
+        d_xb, trb, tcb, ldb, d_local_share, (unsigned)blocks_b, d_xa, tra, tca, lda, d_map_a, share / 4, map_offset / 4, t,
+        rank, epoch, d_counter);
+    SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}
+
 int push_share_launch(const float *d_local_share, int64_t share, int64_t map_offset, const PeerTargets &t, int rank,
                       unsigned int epoch, cudaStream_t stream)
 {

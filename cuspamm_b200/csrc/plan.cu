@@ -566,16 +566,22 @@ static int norm_share_and_push(spamm_plan *p, int b_tile_begin, int b_tile_count
     const float *b_share = p->d_b + (size_t)b_tile_begin * TILE * p->N;
     const int64_t map_offset = (int64_t)b_tile_begin * p->n_tiles;
     int st;
-    if (with_a && p->row_tiles)
-        st = spamm_norm_map_pair_dev(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, b_share, b_tile_count * TILE,
-                                     p->N, p->N, p->d_norm_b + map_offset, p->stream);
-    else
+    if (with_a && p->row_tiles) {
+        // one launch: the share's blocks first, the last of them to finish delivers the share while the rest of the
+        // grid still reads A
+        st = norm_map_pair_push_launch(p->d_a, p->row_tiles * TILE, p->K, p->K, p->d_norm_a, b_share, b_tile_count * TILE,
+                                       p->N, p->N, p->d_norm_b + map_offset, map_offset, t, p->peer_rank, p->peer_epoch,
+                                       p->d_peer_flags + MAX_PEERS, p->stream);
+        if (st) return st;
+        p->launches += 1;
+    } else {
         st = spamm_norm_map_dev(b_share, b_tile_count * TILE, p->N, p->N, p->d_norm_b + map_offset, p->stream);
-    if (st) return st;
-    if ((st = push_share_launch(p->d_norm_b + map_offset, (int64_t)b_tile_count * p->n_tiles, map_offset, t, p->peer_rank,
-                                p->peer_epoch, p->stream)))
-        return st;
-    p->launches += 2;
+        if (st) return st;
+        if ((st = push_share_launch(p->d_norm_b + map_offset, (int64_t)b_tile_count * p->n_tiles, map_offset, t,
+                                    p->peer_rank, p->peer_epoch, p->stream)))
+            return st;
+        p->launches += 2;
+    }
     p->peer_wait_pending = true;
     p->have_lists = p->have_pack = false;
     p->packed_all = false;

@@ -18,7 +18,9 @@
  *     process and GPU, a multi-GPU run is several plans;
  *   - every function returns a spamm_status (0 = success); nothing prints, exits or throws;
  *   - pointers named d_* are device pointers of the plan's GPU, all others are host pointers;
- *   - a plan is not thread-safe; calls on one plan are ordered on the plan's CUDA stream.
+ *   - a plan is not thread-safe; calls on one plan are ordered on the plan's CUDA stream.  Different plans may be
+ *     driven from different host threads: the only process-wide state are small per-device caches (SM counts, the
+ *     address of the built-in scratch array) that every thread fills with the same values.
  */
 #ifndef SPAMM_H
 #define SPAMM_H

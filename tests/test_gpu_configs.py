@@ -1,4 +1,4 @@
-"""The benchmark configurations (BASELINE.json) on the GPU: exact comparison with the CPU checker where it
+"""The benchmark configurations on the GPU: exact comparison with the CPU checker where it
 finishes in seconds, and size-independent properties at the full sizes (survivor counts against the checker's
 count on the same norm maps, dense limit against a float matrix product of the half-rounded inputs, row blocks
 that tile the result, a second call that reproduces the first bit for bit)."""
@@ -32,7 +32,7 @@ def full_check(oracle, A, B, tau):
 
 @pytest.mark.parametrize("tau", [1e-10, 1e-6, 1e-4, 1e-2])
 def test_config2_exponential_decay_sweep(oracle, tau):
-    """Config 2 family at N=4096: a_ij = +-exp(-0.1|i-j|), independent seeds, the sweep's non-zero thresholds."""
+    """Exponential decay at N=4096: a_ij = +-exp(-0.1|i-j|), independent seeds, the sweep's non-zero thresholds."""
     from cuspamm_b200 import gen_signed_exp
 
     n = 4096
@@ -59,7 +59,7 @@ def test_config2_dense_limit_tau_zero():
 
 
 def test_config3_algebraic_decay(oracle):
-    """Config 3 family: a_ij = u_ij/(|i-j|^2+1), u in [-1,1); exact check at N=4096."""
+    """Algebraic decay: a_ij = u_ij/(|i-j|^2+1), u in [-1,1); exact check at N=4096."""
     from cuspamm_b200 import gen_uniform_alg
 
     n = 4096
@@ -69,7 +69,7 @@ def test_config3_algebraic_decay(oracle):
 
 
 def test_config4_lattice(oracle):
-    """Config 4 family on a 16^3 lattice (N=4096): symmetric, list lengths spread over a wide range."""
+    """Density-matrix surrogate on a 16^3 lattice (N=4096): symmetric, list lengths spread over a wide range."""
     from cuspamm_b200 import gen_lattice
 
     A = gen_lattice(16, 7)
@@ -121,7 +121,7 @@ def test_full_size_properties_n16384(oracle):
 
 
 def test_config5_dense_uniform_rows_sample():
-    """Config 5 (dense uniform, tau=0) at N=8192: every product executed, rows checked against a float product."""
+    """Dense uniform matrices, tau=0, at N=8192: every product executed, rows checked against a float product."""
     import torch
 
     from cuspamm_b200 import SpammPlan, gen_uniform

@@ -74,7 +74,7 @@ def test_rectangular(oracle):
 
 
 def test_config1_n1024(oracle):
-    """BASELINE config 1: N=1024, A=B, a_ij = +-exp(-0.5|i-j|), tau=1e-6."""
+    """The smallest benchmark configuration: N=1024, A=B, a_ij = +-exp(-0.5|i-j|), tau=1e-6."""
     from cuspamm_b200 import gen_signed_exp
 
     A = gen_signed_exp(0.5, 1, 1024, 1024)
