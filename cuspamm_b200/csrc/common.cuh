@@ -109,6 +109,14 @@ int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, cons
                                 bool build_records, spamm_list_scalars *d_scalars, int row_tiles, int k_tiles,
                                 int n_tiles, float *d_c, int64_t ldc, int mode, cudaStream_t stream);
 
+// Per source file: load its kernels onto the current device now instead of at their first launch.
+int preload_norm();
+int preload_lists();
+int preload_pack();
+int preload_multiply();
+int preload_multiply_pair();
+int preload_multiply_gpair();
+
 #define SPAMM_CUDA_TRY(call)                                                    \
     do {                                                                        \
         cudaError_t e__ = (call);                                               \

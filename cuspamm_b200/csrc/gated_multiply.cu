@@ -533,6 +533,16 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
     }
 }
 
+// Loads this file's kernels onto the current device now (kernels are loaded lazily, at their first launch, and such
+// a load can wait for kernels that are running; a kernel of one GPU that waits for a peer must not find the peer stuck
+// in the load of a kernel it needs).
+int preload_multiply()
+{
+    cudaFuncAttributes a;
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, gated_multiply_kernel));
+    return SPAMM_OK;
+}
+
 }  // namespace spamm
 
 extern "C" int spamm_gated_multiply_dev(const void *d_half_a, const void *d_half_b, const uint32_t *d_steps,

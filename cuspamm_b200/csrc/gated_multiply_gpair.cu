@@ -596,4 +596,15 @@ int gated_multiply_gpair_launch(const void *d_half_a, const void *d_half_b, cons
     return SPAMM_OK;
 }
 
+// Loads this file's kernels onto the current device now (kernels are loaded lazily, at their first launch, and such
+// a load can wait for kernels that are running; a kernel of one GPU that waits for a peer must not find the peer stuck
+// in the load of a kernel it needs).
+int preload_multiply_gpair()
+{
+    cudaFuncAttributes a;
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, pair_runs_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, gated_multiply_gpair_kernel));
+    return SPAMM_OK;
+}
+
 }  // namespace spamm

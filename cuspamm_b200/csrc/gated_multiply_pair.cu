@@ -427,4 +427,15 @@ int gated_multiply_pair_launch(const void *d_half_a, const void *d_half_b, const
                            sm_count_of[dev], pair_rows * mj_n, stream);
 }
 
+// Loads this file's kernels onto the current device now (kernels are loaded lazily, at their first launch, and such
+// a load can wait for kernels that are running; a kernel of one GPU that waits for a peer must not find the peer stuck
+// in the load of a kernel it needs).
+int preload_multiply_pair()
+{
+    cudaFuncAttributes a;
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, gated_multiply_pair_kernel<1>));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, gated_multiply_pair_kernel<2>));
+    return SPAMM_OK;
+}
+
 }  // namespace spamm

@@ -222,7 +222,16 @@ push_share_kernel(const float4 *__restrict__ src, int64_t vecs, int64_t map_offs
     const int d = blockIdx.x;                       // destination GPU
     if (d != self) {
         float4 *dst = reinterpret_cast<float4 *>(t.map[d]) + map_offset_vecs;
-        for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
+        constexpr int U = 8;                        // eight loads in flight per thread
+        for (int64_t i0 = threadIdx.x; i0 < vecs; i0 += (int64_t)blockDim.x * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (i0 + (int64_t)u * blockDim.x < vecs) v[u] = src[i0 + (int64_t)u * blockDim.x];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (i0 + (int64_t)u * blockDim.x < vecs) dst[i0 + (int64_t)u * blockDim.x] = v[u];
+        }
     }
     __syncthreads();                                // orders the block's stores before the fence below
     if (threadIdx.x == 0) {
@@ -256,11 +265,26 @@ norm_map_pair_push_kernel(const float *__restrict__ xb, int tile_rows_b, int til
     __syncthreads();
     if (ticket != blocks_b - 1) return;
     __threadfence();                                // the last block: everybody else's norms are visible to it
+    // one block moves the whole share: eight loads in flight per thread, each value stored to every peer, so the
+    // copy is bound by the stores over NVLink and not by one L2 round trip per 16 bytes
     const float4 *src = reinterpret_cast<const float4 *>(share);
-    for (int d = 0; d < t.n; d++) {
-        if (d == self) continue;
-        float4 *dst = reinterpret_cast<float4 *>(t.map[d]) + map_offset_vecs;
-        for (int64_t i = threadIdx.x; i < share_vecs; i += blockDim.x) dst[i] = __ldcg(src + i);
+    constexpr int PUSH_UNROLL = 8;
+    for (int64_t i0 = threadIdx.x; i0 < share_vecs; i0 += (int64_t)blockDim.x * PUSH_UNROLL) {
+        float4 v[PUSH_UNROLL];
+#pragma unroll
+        for (int u = 0; u < PUSH_UNROLL; u++) {
+            const int64_t i = i0 + (int64_t)u * blockDim.x;
+            if (i < share_vecs) v[u] = __ldcg(src + i);
+        }
+        for (int d = 0; d < t.n; d++) {
+            if (d == self) continue;
+            float4 *dst = reinterpret_cast<float4 *>(t.map[d]) + map_offset_vecs;
+#pragma unroll
+            for (int u = 0; u < PUSH_UNROLL; u++) {
+                const int64_t i = i0 + (int64_t)u * blockDim.x;
+                if (i < share_vecs) dst[i] = v[u];
+            }
+        }
     }
     __syncthreads();                                // orders the block's stores before the fence below
     if (threadIdx.x == 0) {
@@ -306,6 +330,20 @@ int push_share_launch(const float *d_local_share, int64_t share, int64_t map_off
     push_share_kernel<<<t.n, 256, 0, stream>>>(reinterpret_cast<const float4 *>(d_local_share), share / 4,
                                               map_offset / 4, t, rank, epoch);
     SPAMM_CUDA_TRY(cudaGetLastError());
+    return SPAMM_OK;
+}
+
+// Loads this file's kernels onto the current device now (kernels are loaded lazily, at their first launch, and such
+// a load can wait for kernels that are running; a kernel of one GPU that waits for a peer must not find the peer stuck
+// in the load of a kernel it needs).
+int preload_norm()
+{
+    cudaFuncAttributes a;
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, norm_map_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, norm_map_pair_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, norm_pack_pair_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, push_share_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, norm_map_pair_push_kernel));
     return SPAMM_OK;
 }
 

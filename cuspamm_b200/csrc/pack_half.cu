@@ -118,6 +118,16 @@ pack_half_kernel(const float *__restrict__ a, const float *__restrict__ b, int k
     if (threadIdx.x == 1 && blk_cnt[1]) atomicAdd(&sc->packed_b, blk_cnt[1]);
 }
 
+// Loads this file's kernels onto the current device now (kernels are loaded lazily, at their first launch, and such
+// a load can wait for kernels that are running; a kernel of one GPU that waits for a peer must not find the peer stuck
+// in the load of a kernel it needs).
+int preload_pack()
+{
+    cudaFuncAttributes a;
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, pack_half_kernel));
+    return SPAMM_OK;
+}
+
 }  // namespace spamm
 
 extern "C" int spamm_pack_half_dev(const float *d_a, const float *d_b, int row_tiles, int k_tiles, int n_tiles,

@@ -286,6 +286,13 @@ int spamm_plan_create(spamm_plan **out, int M, int K, int N, int row_tile_begin,
     SPAMM_CUDA_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
     if (cc_major != 10) return SPAMM_ERR_UNSUPPORTED;
 
+    {
+        // every kernel of the path is loaded onto this device before any of them runs (see preload_norm)
+        int st;
+        if ((st = preload_norm()) || (st = preload_lists()) || (st = preload_pack()) || (st = preload_multiply()) ||
+            (st = preload_multiply_pair()) || (st = preload_multiply_gpair()))
+            return st;
+    }
     spamm_plan *p = new (std::nothrow) spamm_plan();
     if (!p) return SPAMM_ERR_ALLOC;
     p->M = M; p->K = K; p->N = N;

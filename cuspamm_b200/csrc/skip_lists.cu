@@ -300,6 +300,18 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
     if (lane == 0 && s) atomicAdd(&sc->survivors, (unsigned long long)s);
 }
 
+// Loads this file's kernels onto the current device now (kernels are loaded lazily, at their first launch, and such
+// a load can wait for kernels that are running; a kernel of one GPU that waits for a peer must not find the peer stuck
+// in the load of a kernel it needs).
+int preload_lists()
+{
+    cudaFuncAttributes a;
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, peer_wait_selftest_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, chunk_max_kernel));
+    SPAMM_CUDA_TRY(cudaFuncGetAttributes(&a, build_lists_kernel));
+    return SPAMM_OK;
+}
+
 }  // namespace spamm
 
 extern "C" size_t spamm_build_lists_scratch_bytes(int row_tiles, int k_tiles, int n_tiles)
