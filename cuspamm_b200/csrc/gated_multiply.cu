@@ -6,13 +6,18 @@
 // Here a persistent block per SM walks macro tiles of 128 x 256 C elements (4 x 8 tiles):
 //
 //   warp 0      scheduler + producer: claims macro tiles from a device-wide work counter (those with steps first),
-//               publishes them to the other warps through a small ring, reads the macro tile's step list and
-//               issues bulk copies (cp.async.bulk, completion on an mbarrier) of the packed half tiles the steps
-//               name into a ring of shared-memory stages; the steps of one k share their copies;
-//   warp 1      the whole warp follows the stages, lane 0 issues tcgen05.mma (M=128, N=32*run, K=16) per run of
-//               adjacent tile columns of a step; the step's row set becomes the instruction's disable-output-lane
-//               mask, so tile rows that did not survive are not touched -- no product outside the lists is ever
-//               added;
+//               publishes them to the other warps through a small ring, then reads the macro tile's step list 32
+//               steps at a time, ONE STEP PER LANE: slot and stage boundaries, the copy extents of every slot and
+//               the list of multiplies every step stands for come out of ballots, shuffles and one prefix sum; the
+//               first lane of a slot issues the slot's bulk copies (cp.async.bulk, completion on an mbarrier) of
+//               the packed half tiles into a ring of shared-memory stages, every lane writes the ready-made
+//               multiplies of its step (instruction descriptor, operand descriptors, accumulator column, row set)
+//               into the stage's control block; the steps of one k share their copies;
+//   warp 1      follows the stages and issues what the control block lists: tcgen05.mma (M=128, N=32*run, K=16),
+//               two per entry; the step's row set is the instruction's disable-output-lane mask, so tile rows
+//               that did not survive are not touched -- no product outside the lists is ever added.  The warp
+//               does no decoding: one thread that decodes steps AND issues was the limit of this kernel on long
+//               half-full lists (the loop over a stage's entries runs in all lanes, lane 0 issues);
 //   warps 6-9   fillers: when few macro tiles have steps, write the all-zero macro tiles from the start, in
 //               parallel with the pipeline;
 //   warps 2-5   epilogue: read the 128x256 float accumulator from tensor memory (tcgen05.ld), turn it through a
@@ -32,9 +37,9 @@ namespace spamm {
 
 // A stage of the ring holds SPS slots; a slot holds the operands of ONE k of one macro tile (8 KiB of A, 16 KiB of B)
 // and up to GSTEPS steps of that k (steps of the same k differ only in which rows and columns take part, so they
-// share the slab copies).  The thread that issues the
-// multiplies pays a fixed price per stage (barrier wait, commit) and about 110 cycles per tcgen05.mma, against 128
-// cycles of tensor-pipe time for an N=256 instruction, so several steps share one wait and one commit.
+// share the slab copies; their row sets are nested, so a k has at most 4 steps).  Both the producer and the
+// issuing thread pay a fixed price per stage (barrier wait, arrive or commit), so several k share a stage: with one
+// k per stage the lattice workload takes 30 ms instead of 22.
 #ifndef SPAMM_SPS
 #define SPAMM_SPS 2
 #endif
@@ -48,7 +53,8 @@ constexpr int GSTEPS = 4;                                    // steps of one k t
 constexpr int GM_THREADS = 320;                            // producer, MMA, 4 epilogue warps, 4 filler warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = MT_C * TILE;                  // 256
-constexpr int SMEM_CTRL_BYTES = 640;
+constexpr int MAX_OPS = SPS * GSTEPS * 4;                   // a step has at most 4 runs of adjacent columns
+constexpr int SMEM_CTRL_BYTES = 640 + STAGES * MAX_OPS * 16;
 constexpr int SCHED = 4;                                    // depth of the ring of scheduled macro tiles
 constexpr int GM_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 4 * EPI_WARP_BYTES + 128;
 
@@ -64,7 +70,8 @@ struct Ctrl {
     uint32_t filler_base[2];
     int32_t tile_slot[SCHED];
     int32_t tile_cnt[SCHED];
-    uint32_t step_word[STAGES][SPS][GSTEPS];                  // per stage slot: the steps of one k, zero terminated
+    alignas(16) uint4 ops[STAGES][MAX_OPS];                     // per stage: the multiplies to issue, ready-made
+    uint32_t n_ops[STAGES];
     uint32_t stage_last[STAGES];                               // this stage ends its macro tile
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -247,95 +254,141 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             const uint32_t *list = steps + (int64_t)mt * cap;
             const uint8_t *a_base = half_a + (int64_t)mi * k_tiles * A_SLAB_BYTES;
             const uint8_t *b_base = half_b + (int64_t)mj * B_SLAB_BYTES;
-            // lane 0 assembles stages: consecutive steps with the same k go to one slot and share one copy of the A
-            // slab and one of the B columns they span; a stage is sent off when its slots are full or the list ends
-            uint32_t sw[SPS][GSTEPS];
-            uint32_t rows_u[SPS], cols_u[SPS];
-            int n_slots = 0, n_in_slot = 0;
-            auto flush_stage = [&](bool last) {
-                const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
-                ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, ERR_WAIT_EMPTY);
-                if (!ok) return;
-                const uint32_t bar = smem_u32(&ctrl->full[s]);
-                const uint32_t a_stage = smem_u32(smem + s * STAGE_BYTES);
-                const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
-                uint32_t bytes = 0;
-                uint32_t a_bytes[SPS], b_first[SPS], b_len[SPS];
-#pragma unroll
-                for (int t = 0; t < SPS; t++) {
-#pragma unroll
-                    for (int g = 0; g < GSTEPS; g++) ctrl->step_word[s][t][g] = (t < n_slots) ? sw[t][g] : 0u;
-                    a_bytes[t] = b_first[t] = b_len[t] = 0;
-                    if (t < n_slots) {
-                        // A: one tile when a single row takes part, else the whole slab in one copy
-                        a_bytes[t] = (__popc(rows_u[t]) == 1) ? TILE_BYTES : A_SLAB_BYTES;
-                        // B: everything from the first to the last column that takes part, in one copy
-                        b_first[t] = (uint32_t)(__ffs(cols_u[t]) - 1);
-                        b_len[t] = (uint32_t)(32 - __clz(cols_u[t])) - b_first[t];
-                        bytes += a_bytes[t] + b_len[t] * TILE_BYTES;
+            // The whole warp assembles stages, 32 steps at a time, one step per lane: consecutive steps with the same
+            // k form a slot (they share one copy of the A slab and one of the B columns they span), SPS slots a
+            // stage.  Slot boundaries, the slots' unions of rows and columns and their copy extents come from
+            // ballots and shuffles; the first lane of a slot writes the slot's control words and issues its copies;
+            // lane 0 waits for the stage to be free before and arrives on its barrier after.
+            uint32_t cur = (lane < cnt) ? __ldg(list + lane) : 0u;
+            uint32_t nxt = (32 + lane < cnt) ? __ldg(list + 32 + lane) : 0u;
+            for (int base = 0; base < cnt && ok;) {
+                const int n_here = min(32, cnt - base);
+                const bool more = base + 32 < cnt;
+                const bool valid = lane < n_here;
+                const uint32_t k = step_k(cur);
+                const uint32_t k_prev = __shfl_up_sync(0xffffffffu, k, 1);
+                const uint32_t k_heads = __ballot_sync(0xffffffffu, valid && (lane == 0 || k != k_prev));
+                // position inside the run of equal k; a run longer than GSTEPS goes on in a further slot
+                const int run_start = 31 - __clz(k_heads & (0xffffffffu >> (31 - lane)));
+                const bool head = valid && (((lane - run_start) % GSTEPS) == 0);
+                uint32_t heads = __ballot_sync(0xffffffffu, head);
+                int used = n_here;
+                if (more) {
+                    // the last slot may go on in the next batch: leave it (and one more, to fill whole stages) for then
+                    int n_sl = __popc(heads);
+                    int drop = (n_sl >= 2) ? 1 : 0;
+                    if (drop && ((n_sl - drop) % SPS) != 0 && n_sl - drop > 1) drop++;
+                    for (int x = 0; x < drop; x++) {
+                        const int hl = 31 - __clz(heads);
+                        used = hl;
+                        heads &= ~(1u << hl);
                     }
                 }
-                ctrl->stage_last[s] = last ? 1u : 0u;
-                mbar_arrive_expect_tx(bar, bytes);
-                bool a_done = false;
-                if (SPS >= 2 && n_slots >= 2 && a_bytes[0] == A_SLAB_BYTES && a_bytes[1] == A_SLAB_BYTES &&
-                    step_k(sw[1][0]) == step_k(sw[0][0]) + 1u) {
-                    // two slabs of consecutive k are neighbours in memory
-                    bulk_g2s(a_stage, a_base + (int64_t)step_k(sw[0][0]) * A_SLAB_BYTES, 2 * A_SLAB_BYTES, bar);
-                    a_done = true;
-                }
+                const bool last_batch = !more || base + used >= cnt;
+                const int n_slots = __popc(heads);
+                const int slot_idx = __popc(heads & (0xffffffffu >> (31 - lane))) - 1;      // of this lane's step
+                // steps of this lane's slot, gathered into its first lane
+                const uint32_t ends = (heads | (used < 32 ? (0xffffffffu << used) : 0u));
+                uint32_t w1 = __shfl_down_sync(0xffffffffu, cur, 1);
+                uint32_t w2 = __shfl_down_sync(0xffffffffu, cur, 2);
+                uint32_t w3 = __shfl_down_sync(0xffffffffu, cur, 3);
+                // number of steps in a slot that starts here: distance to the next slot start (or the end of the batch)
+                const uint32_t after = (lane < 31) ? (ends >> (lane + 1)) : 0u;
+                const int dist = after ? __ffs(after) : (32 - lane);
+                if (dist < 2) w1 = 0u;
+                if (dist < 3) w2 = 0u;
+                if (dist < 4) w3 = 0u;
+                const bool is_head = (heads >> lane) & 1u;
+                const uint32_t all = cur | w1 | w2 | w3;
+                const uint32_t rows_u = step_rows(all), cols_u = step_cols(all);
+                const uint32_t a_bytes = (__popc(rows_u) == 1) ? TILE_BYTES : A_SLAB_BYTES;
+                const uint32_t b_first = (uint32_t)(__ffs(cols_u) - 1);
+                const uint32_t b_len = (uint32_t)(32 - __clz(cols_u)) - b_first;
+                const int n_stages = (n_slots + SPS - 1) / SPS;
+                // two slots of one stage whose k are neighbours and that need whole slabs of A: the slabs are
+                // neighbours in memory too, and the first slot's lane fetches both with one copy
+                const int next_head = (lane + dist) & 31;
+                const uint32_t k_nh = __shfl_sync(0xffffffffu, k, next_head);
+                const uint32_t ab_nh = __shfl_sync(0xffffffffu, a_bytes, next_head);
+                const bool merge_next = SPS == 2 && is_head && (slot_idx % SPS) == 0 && slot_idx + 1 < n_slots &&
+                                        a_bytes == A_SLAB_BYTES && ab_nh == A_SLAB_BYTES && k_nh == k + 1u;
+                const uint32_t before = heads & ((1u << lane) - 1u);
+                const int prev_head = before ? (31 - __clz(before)) : 0;
+                const bool merged_prev = __shfl_sync(0xffffffffu, merge_next ? 1 : 0, prev_head) != 0 && is_head &&
+                                         (slot_idx % SPS) == 1;
+                // every lane turns its step into the multiplies it stands for: one per run of adjacent columns
+                const bool in_use = lane < used;
+                const uint32_t my_rows = step_rows(cur), my_cols = in_use ? step_cols(cur) : 0u;
+                const int n_runs = __popc(my_cols & ~(my_cols << 1));
+                int incl = n_runs;
 #pragma unroll
-                for (int t = 0; t < SPS; t++) {
-                    if (t >= n_slots) break;
-                    const uint32_t k = step_k(sw[t][0]);
-                    const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
-                    const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
-                    if (a_done && t < 2) {
-                    } else if (a_bytes[t] == A_SLAB_BYTES) {
-                        bulk_g2s(a_stage + t * A_SLAB_BYTES, a_src, A_SLAB_BYTES, bar);
-                    } else {
-                        const uint32_t q = (uint32_t)(__ffs(rows_u[t]) - 1);
-                        bulk_g2s(a_stage + t * A_SLAB_BYTES + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
-                    }
-                    bulk_g2s(b_stage + t * B_SLAB_BYTES + b_first[t] * TILE_BYTES, b_src + b_first[t] * TILE_BYTES,
-                             b_len[t] * TILE_BYTES, bar);
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int tt = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= d) incl += tt;
                 }
-                slot++;
-                n_slots = 0;
-                n_in_slot = 0;
-            };
-            uint32_t next = (lane < cnt) ? __ldg(list + lane) : 0u;
-            for (int i0 = 0; i0 < cnt && ok; i0 += 32) {
-                const uint32_t mine = next;
-                // fetch the following batch of steps while these are being issued
-                next = (i0 + 32 + lane < cnt) ? __ldg(list + i0 + 32 + lane) : 0u;
-                const int nb = min(32, cnt - i0);
-                for (int j = 0; j < nb; j++) {
-                    const uint32_t w = __shfl_sync(0xffffffffu, mine, j);
-                    if (lane == 0) {
-                        const bool same_k = n_in_slot > 0 && n_in_slot < GSTEPS && step_k(sw[n_slots - 1][0]) == step_k(w);
-                        if (!same_k) {
-                            if (n_slots == SPS) flush_stage(false);
-                            if (ok) {
-                                n_slots++;
-                                n_in_slot = 0;
-                                rows_u[n_slots - 1] = cols_u[n_slots - 1] = 0;
-#pragma unroll
-                                for (int g = 0; g < GSTEPS; g++) sw[n_slots - 1][g] = 0u;
-                            }
-                        }
-                        if (ok) {
-                            sw[n_slots - 1][n_in_slot++] = w;
-                            rows_u[n_slots - 1] |= step_rows(w);
-                            cols_u[n_slots - 1] |= step_cols(w);
-                        }
-                    }
+                const int my_stage = slot_idx / SPS;
+                const uint32_t stage_heads = __ballot_sync(0xffffffffu, is_head && (slot_idx % SPS) == 0);
+                const int st_first = 31 - __clz(stage_heads & (0xffffffffu >> (31 - lane)));
+                const uint32_t st_ends = stage_heads | (used < 32 ? (0xffffffffu << used) : 0u);
+                const uint32_t st_after = (lane < 31) ? (st_ends >> (lane + 1)) : 0u;
+                const int st_last = st_after ? (lane + __ffs(st_after) - 1) : 31;
+                const int excl_first = __shfl_sync(0xffffffffu, incl - n_runs, st_first & 31);
+                const int incl_last = __shfl_sync(0xffffffffu, incl, st_last & 31);
+                const int my_pos = incl - n_runs - excl_first;
+                const int stage_total = incl_last - excl_first;      // meaningful in the first lane of a stage
+                for (int j = 0; j < n_stages && ok; j++) {
+                    const uint32_t s = slot % STAGES, ph = (slot / STAGES) & 1u;
+                    if (lane == 0) ok = wait_bounded(smem_u32(&ctrl->empty[s]), ph ^ 1u, abort_flag, err, ERR_WAIT_EMPTY);
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
+                    const uint32_t bar = smem_u32(&ctrl->full[s]);
+                    if (in_use && my_stage == j) {
+                        const int t = slot_idx % SPS;
+                        const uint32_t a_stage = smem_u32(smem + s * STAGE_BYTES);
+                        const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+                        const uint32_t a_addr = a_stage + t * A_SLAB_BYTES, b_addr = b_stage + t * B_SLAB_BYTES;
+                        if (is_head) {
+                            const uint8_t *a_src = a_base + (int64_t)k * A_SLAB_BYTES;
+                            const uint8_t *b_src = b_base + (int64_t)k * mj_n * B_SLAB_BYTES;
+                            mbar_expect_tx(bar, (merged_prev ? 0u : a_bytes) + (merge_next ? A_SLAB_BYTES : 0u) +
+                                                    b_len * TILE_BYTES);
+                            if (merged_prev) {
+                            } else if (a_bytes == A_SLAB_BYTES) {
+                                bulk_g2s(a_addr, a_src, merge_next ? 2 * A_SLAB_BYTES : A_SLAB_BYTES, bar);
+                            } else {
+                                const uint32_t q = (uint32_t)(__ffs(rows_u) - 1);
+                                bulk_g2s(a_addr + q * TILE_BYTES, a_src + q * TILE_BYTES, TILE_BYTES, bar);
+                            }
+                            bulk_g2s(b_addr + b_first * TILE_BYTES, b_src + b_first * TILE_BYTES, b_len * TILE_BYTES, bar);
+                        }
+                        uint32_t rest = my_cols;
+                        int pos = my_pos;
+                        while (rest) {
+                            const int c0 = __ffs(rest) - 1;
+                            const int len = __ffs(~(rest >> c0)) - 1;
+                            const uint32_t n = (uint32_t)len * TILE;
+                            const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+                            ctrl->ops[s][pos++] = make_uint4(idesc, (b_addr + (uint32_t)c0 * TILE_BYTES) >> 4,
+                                                             (uint32_t)c0 * TILE, my_rows | ((a_addr >> 4) << 4));
+                            rest &= ~(((1u << len) - 1u) << c0);
+                        }
+                        if (is_head && t == 0) {
+                            ctrl->n_ops[s] = (uint32_t)stage_total;
+                            ctrl->stage_last[s] = (last_batch && j == n_stages - 1) ? 1u : 0u;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar);
+                    slot++;
                 }
+                // the next 32 steps start `used` further on: part of them is already here
+                base += used;
+                const uint32_t from_cur = __shfl_sync(0xffffffffu, cur, (lane + used) & 31);
+                const uint32_t from_nxt = __shfl_sync(0xffffffffu, nxt, (lane + used) & 31);
+                cur = (lane + used < 32) ? from_cur : from_nxt;
+                nxt = (base + 32 + lane < cnt) ? __ldg(list + base + 32 + lane) : 0u;
+                if (used == 32) { /* cur is the old nxt entirely: handled by the select above */ }
             }
-            if (lane == 0 && ok && n_slots > 0) flush_stage(true);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         if (lane == 0 && *abort_flag) {
             // make sure every copy this block issued has landed before the block can exit
@@ -355,8 +408,6 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             bool ok = true;
             // descriptor without the start address: adding (address >> 4) completes it, +16 is the second K=16 half
             const uint64_t desc0 = smem_desc(0);
-            const uint32_t stage0 = smem_u32(smem);
-            constexpr uint32_t IDESC_N256 = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
             for (uint32_t sidx = 0; ok; sidx++) {
                 const uint32_t d = sidx % SCHED, sph = (sidx / SCHED) & 1u;
                 ok = wait_bounded(smem_u32(&ctrl->sched_full[d]), sph, abort_flag, err, ERR_WAIT_SCHED_FULL);
@@ -379,45 +430,26 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
                     if (!ok) break;
                     tc_fence_after();
                     last = ctrl->stage_last[s] != 0u;
-                    const uint32_t a_stage = stage0 + s * STAGE_BYTES;
-                    const uint32_t b_stage = a_stage + SPS * A_SLAB_BYTES;
+                    const uint32_t n_ops = ctrl->n_ops[s];
                     __syncwarp();       // every lane has read the stage's control words before lane 0 can release it
-                    if (lane == 0) {
-#pragma unroll
-                    for (int t = 0; t < SPS; t++) {
-                        const uint32_t a_addr = a_stage + t * A_SLAB_BYTES;
-                        const uint32_t b_addr = b_stage + t * B_SLAB_BYTES;
-                        const uint64_t da = desc0 + (uint64_t)(a_addr >> 4);
+                    {
+                        // every lane follows the list of multiplies (the values are the same in all lanes); lane 0 issues
+                        uint4 op = ctrl->ops[s][0];
 #pragma unroll 1
-                        for (int g = 0; g < GSTEPS; g++) {
-                            const uint32_t w = ctrl->step_word[s][t][g];
-                            if (w == 0u) break;
-                            if ((w >> 16) == 0xfffu) {
-                                // every row and every column of the macro tile: two instructions with N = 256
-                                const uint64_t db = desc0 + (uint64_t)(b_addr >> 4);
-                                umma_f16_all_rows(dbase, da, db, IDESC_N256);
-                                umma_f16_all_rows(dbase, da + 16u, db + 16u, IDESC_N256);
-                            } else {
-                                const uint32_t rows = step_rows(w), cols = step_cols(w);
-                                const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
-                                const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
-                                uint32_t rest = cols;
-                                while (rest) {
-                                    const int c0 = __ffs(rest) - 1;
-                                    const uint32_t shifted = rest >> c0;
-                                    const int len = __ffs(~shifted) - 1;
-                                    const uint32_t n = (uint32_t)len * TILE;
-                                    const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-                                    const uint64_t db = desc0 + (uint64_t)((b_addr + (uint32_t)c0 * TILE_BYTES) >> 4);
-                                    const uint32_t dcol = dbase + (uint32_t)c0 * TILE;
-                                    umma_f16(dcol, da, db, idesc, m0, m1, m2, m3);
-                                    umma_f16(dcol, da + 16u, db + 16u, idesc, m0, m1, m2, m3);
-                                    rest &= ~(((1u << len) - 1u) << c0);
-                                }
+                        for (uint32_t i = 0; i < n_ops; i++) {
+                            const uint4 nx = ctrl->ops[s][min(i + 1u, (uint32_t)MAX_OPS - 1u)];
+                            const uint32_t rows = op.w & 0xfu;
+                            const uint64_t da = desc0 + (uint64_t)(op.w >> 4), db = desc0 + (uint64_t)op.y;
+                            const uint32_t dcol = dbase + op.z;
+                            const uint32_t m0 = (rows & 1u) ? 0u : 0xffffffffu, m1 = (rows & 2u) ? 0u : 0xffffffffu;
+                            const uint32_t m2 = (rows & 4u) ? 0u : 0xffffffffu, m3 = (rows & 8u) ? 0u : 0xffffffffu;
+                            if (lane == 0) {
+                                umma_f16(dcol, da, db, op.x, m0, m1, m2, m3);
+                                umma_f16(dcol, da + 16u, db + 16u, op.x, m0, m1, m2, m3);
                             }
+                            op = nx;
                         }
-                    }
-                    umma_commit(smem_u32(&ctrl->empty[s]));
+                        if (lane == 0) umma_commit(smem_u32(&ctrl->empty[s]));
                     }
                     __syncwarp();
                     slot++;
