@@ -539,15 +539,22 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             const bool row_ok = row < rows_total;
             // first row of this warp's 32-row block of C, first column of the macro tile
             float *cblock = c + (int64_t)(row - lane) * ldc + (int64_t)mj * (MT_C * TILE);
+            // two register sets: the load of the next block of 32 columns is under way while the current one is stored
+            const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS;
+            uint32_t v0[32], v1[32];
+            tmem_ld32(tacc, v0);
 #pragma unroll 1
-            for (int cc = 0; cc < MT_C; cc++) {
-                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS + (uint32_t)cc * TILE;
-                uint32_t v[32];
-                tmem_ld32(taddr, v);
+            for (int cc = 0; cc < MT_C; cc += 2) {
                 tmem_wait_ld();
-                tmem_st32_zero(taddr);
+                tmem_ld32(tacc + (uint32_t)(cc + 1) * TILE, v1);
+                tmem_st32_zero(tacc + (uint32_t)cc * TILE);
                 if (row_ok && mj * MT_C + cc < n_tiles)
-                    store_block_coalesced(epi_tile, v, cblock + cc * TILE, ldc, lane, accumulate, acc_scale);
+                    store_block_coalesced(epi_tile, v0, cblock + cc * TILE, ldc, lane, accumulate, acc_scale);
+                tmem_wait_ld();
+                if (cc + 2 < MT_C) tmem_ld32(tacc + (uint32_t)(cc + 2) * TILE, v0);
+                tmem_st32_zero(tacc + (uint32_t)(cc + 1) * TILE);
+                if (row_ok && mj * MT_C + cc + 1 < n_tiles)
+                    store_block_coalesced(epi_tile, v1, cblock + (cc + 1) * TILE, ldc, lane, accumulate, acc_scale);
             }
             tmem_wait_st();
             tc_fence_before();

@@ -92,7 +92,8 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 static __device__ __noinline__ bool wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
                                                   int32_t *err, int code)
 {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (mbar_try_wait_cluster(bar, parity) || mbar_try_wait_cluster(bar, parity) || mbar_try_wait_cluster(bar, parity))
+        return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         if (mbar_try_wait_cluster(bar, parity)) return true;

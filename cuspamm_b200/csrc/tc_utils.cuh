@@ -50,6 +50,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 static __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int32_t *err,
                                        int code)
 {
+    // a try_wait suspends the thread for a while by itself: most waits end in one of these, before the (slow to read)
+    // global timer is needed at all
+    if (mbar_try_wait(bar, parity) || mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
