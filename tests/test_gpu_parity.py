@@ -73,6 +73,27 @@ def test_rectangular(oracle):
     check_against_oracle(oracle, A, B, 0.6)
 
 
+@pytest.mark.parametrize("tau", [1e-6, 1e-4, 3e-3])
+def test_ragged_steps_across_list_batches(oracle, tau):
+    """Tile magnitudes spread over six decades, independently per tile: a k then has up to four steps (nested row
+    sets) whose columns fall into several runs, a macro tile's list is several times 32 steps long (the multiply
+    kernel reads it 32 steps at a time and a k's steps may straddle two reads), and the last macro tile row and
+    column are cut (9 x 48 x 17 tiles)."""
+    rng = np.random.default_rng(41)
+    M, K, N = 288, 1536, 544
+
+    def ragged(rows, cols):
+        x = rng.standard_normal((rows, cols)).astype(np.float32)
+        scale = np.power(10.0, -6.0 * rng.random((rows // 32, cols // 32))).astype(np.float32)
+        return (x.reshape(rows // 32, 32, cols // 32, 32) * scale[:, None, :, None]).reshape(rows, cols) / 32
+
+    A, B = ragged(M, K), ragged(K, N)
+    got, _ = check_against_oracle(oracle, A, B, tau)
+    # the case is what it claims to be: lists longer than one read, and tiles with partly filled lists
+    assert got["counts"].max() > 8
+    assert 0 < got["S"] < (M // 32) * (K // 32) * (N // 32)
+
+
 def test_config1_n1024(oracle):
     """The smallest benchmark configuration: N=1024, A=B, a_ij = +-exp(-0.5|i-j|), tau=1e-6."""
     from cuspamm_b200 import gen_signed_exp
