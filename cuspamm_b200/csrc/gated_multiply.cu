@@ -184,7 +184,11 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
         // chosen for operand reuse in L2, is used for everything.
         const unsigned int busy_n = sc->busy_count;
         const bool use_busy = busy_n * 4u <= n_mt;
-        const unsigned int chunk = use_busy ? 4u : 1u;     // zero-only macro tiles are claimed four at a time
+        // zero-only macro tiles are claimed four at a time; so are macro tiles with short lists when there are many per
+        // SM (a claim is a chain of three dependent reads before the first copy can be issued; long lists keep the
+        // one-by-one order, which is the one chosen for operand reuse in L2)
+        const bool short_lists = sc->survivors < 256ull * n_mt && n_mt >= 16u * gridDim.x;
+        const unsigned int chunk = (use_busy || short_lists) ? 4u : 1u;
         int phase = use_busy ? 1 : 2;
         int cand_mt = -1, cand_cnt = 0;                    // per lane: candidates of the claimed chunk
         uint32_t pending = 0;                              // lanes whose candidate is still to be scheduled

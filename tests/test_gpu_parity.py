@@ -94,6 +94,28 @@ def test_ragged_steps_across_list_batches(oracle, tau):
     assert 0 < got["S"] < (M // 32) * (K // 32) * (N // 32)
 
 
+def test_random_shapes_and_magnitudes(oracle):
+    """Two dozen seeded cases of random tile counts (1-13 x 1-259 x 1-39), spreads of the tile magnitudes (half a
+    decade to eight) and thresholds: lists bit-equal, C within tolerance, whatever mix of full, partial and empty
+    steps, runs of columns and list lengths comes out."""
+    rng = np.random.default_rng(2024)
+
+    def ragged(rows, cols, decades):
+        x = rng.standard_normal((rows, cols)).astype(np.float32)
+        scale = np.power(10.0, -decades * rng.random((rows // 32, cols // 32))).astype(np.float32)
+        return (x.reshape(rows // 32, 32, cols // 32, 32) * scale[:, None, :, None]).reshape(rows, cols) / 32
+
+    survivors = []
+    for _ in range(24):
+        mt, kt, nt = int(rng.integers(1, 14)), int(rng.integers(1, 260)), int(rng.integers(1, 40))
+        decades = float(rng.choice([0.5, 2, 4, 6, 8]))
+        tau = float(10.0 ** rng.uniform(-7, -0.5))
+        A, B = ragged(32 * mt, 32 * kt, decades), ragged(32 * kt, 32 * nt, decades)
+        got, _ = check_against_oracle(oracle, A, B, tau)
+        survivors.append(got["S"] / (mt * kt * nt))
+    assert min(survivors) < 0.05 and max(survivors) > 0.5     # the cases span nearly empty to mostly full
+
+
 def test_config1_n1024(oracle):
     """The smallest benchmark configuration: N=1024, A=B, a_ij = +-exp(-0.5|i-j|), tau=1e-6."""
     from cuspamm_b200 import gen_signed_exp
