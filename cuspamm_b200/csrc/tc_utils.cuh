@@ -137,30 +137,44 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 constexpr int EPI_ROW_BYTES = 144;
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;          // 4608 bytes per epilogue warp
 
-// With `add` the block, times `scale` (a power of two), is added to what C holds.
-__device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const uint32_t *v, float *c_block,
-                                                      int64_t ldc, int lane, bool add = false, float scale = 1.0f)
+// With `add` the block, times `scale` (a power of two), is added to what C holds.  The old values are all requested
+// before anything else happens: issued one by one between the stores (the compiler cannot move a load of C above a
+// store to C) they cost a round trip to L2 or DRAM each, eight per block.
+template <bool add>
+__device__ __forceinline__ void store_block_coalesced_impl(uint8_t *warp_tile, const uint32_t *v, float *c_block,
+                                                           int64_t ldc, int lane, float scale)
 {
+    const int sub = lane >> 3, part = lane & 7;               // four rows per instruction, eight lanes per row
+    float4 old[8];
+    if (add) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            old[i] = __ldcs(reinterpret_cast<const float4 *>(c_block + (int64_t)(4 * i + sub) * ldc + part * 4));
+    }
     uint4 *mine = reinterpret_cast<uint4 *>(warp_tile + lane * EPI_ROW_BYTES);
 #pragma unroll
     for (int x = 0; x < 8; x++) mine[x] = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
     __syncwarp();
-    const int sub = lane >> 3, part = lane & 7;               // four rows per instruction, eight lanes per row
 #pragma unroll
-    for (int r0 = 0; r0 < 32; r0 += 4) {
-        const int r = r0 + sub;
+    for (int i = 0; i < 8; i++) {
+        const int r = 4 * i + sub;
         float4 o = *reinterpret_cast<const float4 *>(warp_tile + r * EPI_ROW_BYTES + part * 16);
         float4 *dst = reinterpret_cast<float4 *>(c_block + (int64_t)r * ldc + part * 4);
         if (add) {
-            const float4 old = *dst;
-            o.x = __fmaf_rn(o.x, scale, old.x);
-            o.y = __fmaf_rn(o.y, scale, old.y);
-            o.z = __fmaf_rn(o.z, scale, old.z);
-            o.w = __fmaf_rn(o.w, scale, old.w);
+            o.x = __fmaf_rn(o.x, scale, old[i].x);
+            o.y = __fmaf_rn(o.y, scale, old[i].y);
+            o.z = __fmaf_rn(o.z, scale, old[i].z);
+            o.w = __fmaf_rn(o.w, scale, old[i].w);
         }
         __stcs(dst, o);
     }
     __syncwarp();
+}
+__device__ __forceinline__ void store_block_coalesced(uint8_t *warp_tile, const uint32_t *v, float *c_block,
+                                                      int64_t ldc, int lane, bool add = false, float scale = 1.0f)
+{
+    if (add) store_block_coalesced_impl<true>(warp_tile, v, c_block, ldc, lane, scale);
+    else store_block_coalesced_impl<false>(warp_tile, v, c_block, ldc, lane, scale);
 }
 
 }  // namespace spamm
