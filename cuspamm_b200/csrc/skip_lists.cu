@@ -125,16 +125,25 @@ chunk_max_kernel(const float *__restrict__ norm_a, const float *__restrict__ nor
     }
 }
 
-// Sets bits of a flag byte and returns the bits that were not set before.
-__device__ __forceinline__ uint32_t or_flag_byte(uint8_t *base, int64_t idx, uint32_t bits)
+// Sets bits of two flag bytes and returns, for each, the bits that were not set before.  Both words are read before
+// either is looked at and both atomics are issued before either result is used: the two round trips overlap.
+__device__ __forceinline__ void or_flag_bytes(uint8_t *base_a, int64_t idx_a, uint32_t bits_a, uint8_t *base_b,
+                                              int64_t idx_b, uint32_t bits_b, uint32_t *new_a, uint32_t *new_b)
 {
-    const uintptr_t addr = reinterpret_cast<uintptr_t>(base) + (uintptr_t)idx;
-    unsigned int *w = reinterpret_cast<unsigned int *>(addr & ~uintptr_t(3));
-    const unsigned int sh = 8 * (unsigned)(addr & 3);
-    const unsigned int v = bits << sh;
-    if ((*reinterpret_cast<volatile unsigned int *>(w) & v) == v) return 0;
-    const unsigned int old = atomicOr(w, v);
-    return ((v & ~old) >> sh) & 0xffu;
+    const uintptr_t addr_a = reinterpret_cast<uintptr_t>(base_a) + (uintptr_t)idx_a;
+    const uintptr_t addr_b = reinterpret_cast<uintptr_t>(base_b) + (uintptr_t)idx_b;
+    unsigned int *wa = reinterpret_cast<unsigned int *>(addr_a & ~uintptr_t(3));
+    unsigned int *wb = reinterpret_cast<unsigned int *>(addr_b & ~uintptr_t(3));
+    const unsigned int sha = 8 * (unsigned)(addr_a & 3), shb = 8 * (unsigned)(addr_b & 3);
+    const unsigned int va = bits_a << sha, vb = bits_b << shb;
+    const unsigned int seen_a = *reinterpret_cast<volatile unsigned int *>(wa);
+    const unsigned int seen_b = *reinterpret_cast<volatile unsigned int *>(wb);
+    const bool do_a = (seen_a & va) != va, do_b = (seen_b & vb) != vb;
+    unsigned int old_a = va, old_b = vb;
+    if (do_a) old_a = atomicOr(wa, va);
+    if (do_b) old_b = atomicOr(wb, vb);
+    *new_a = ((va & ~old_a) >> sha) & 0xffu;
+    *new_b = ((vb & ~old_b) >> shb) & 0xffu;
 }
 
 __global__ void __launch_bounds__(128)
@@ -239,10 +248,9 @@ build_lists_kernel(const float *__restrict__ norm_a, const float *__restrict__ n
             }
             // tiles named for the first time go to the conversion list
             uint32_t new_a = 0, new_b = 0;
-            if (rows_any) {
-                new_a = or_flag_byte(need_a, (int64_t)mi * k_tiles + k, rows_any);
-                new_b = or_flag_byte(need_b, (int64_t)k * mj_n + mj, cols_any);
-            }
+            if (rows_any)
+                or_flag_bytes(need_a, (int64_t)mi * k_tiles + k, rows_any, need_b, (int64_t)k * mj_n + mj, cols_any, &new_a,
+                              &new_b);
             const int n_new = __popc(new_a) + __popc(new_b);
             // two warp prefix sums at once: steps (low 16 bits) and new tiles (high 16 bits); both are <= 12 per lane
             uint32_t incl = (uint32_t)n | ((uint32_t)n_new << 16);
