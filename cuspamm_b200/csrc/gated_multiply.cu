@@ -261,8 +261,9 @@ gated_multiply_kernel(const uint8_t *__restrict__ half_a, const uint8_t *__restr
             // The whole warp assembles stages, 32 steps at a time, one step per lane: consecutive steps with the same
             // k form a slot (they share one copy of the A slab and one of the B columns they span), SPS slots a
             // stage.  Slot boundaries, the slots' unions of rows and columns and their copy extents come from
-            // ballots and shuffles; the first lane of a slot writes the slot's control words and issues its copies;
-            // lane 0 waits for the stage to be free before and arrives on its barrier after.
+            // ballots and shuffles; the first lane of a slot issues the slot's copies, every lane writes the
+            // multiplies of its own step into the stage's list; lane 0 waits for the stage to be free before and
+            // arrives on its barrier after.
             uint32_t cur = (lane < cnt) ? __ldg(list + lane) : 0u;
             uint32_t nxt = (32 + lane < cnt) ? __ldg(list + 32 + lane) : 0u;
             for (int base = 0; base < cnt && ok;) {
